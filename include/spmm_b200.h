@@ -1,0 +1,136 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of the bitmap-v3 sparse SpMM path.
+ *
+ * Every entry point is extern "C" with plain pointers and sizes.  Each one names
+ * the reference interface it replaces (path inside the reference project:line).
+ * The same shared library also exports the reference's own C++-mangled symbols
+ * (declared in include/SpMM_API.cuh) so that code written against the reference
+ * header links unchanged.
+ *
+ * Conventions
+ *   - fp16 values travel as uint16_t bit patterns.
+ *   - "stream" is a cudaStream_t passed as void*.
+ *   - A is M x K row-major; B is K x N column-major (stored [N][K]); C is M x N
+ *     column-major (stored [N][M]).  M and K must be multiples of 64.
+ *   - Functions returning int return 0 (cudaSuccess) or a cudaError_t value,
+ *     unless stated otherwise; spb_last_error() gives a message for the calling
+ *     thread's last failure.
+ *   - There is no CPU fallback: without a usable CUDA device every compute
+ *     entry point fails.
+ */
+#ifndef SPMM_B200_H
+#define SPMM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Library version (major*10000 + minor*100 + patch). */
+int spb_version(void);
+
+/* Message describing the calling thread's most recent failure ("" if none). */
+const char* spb_last_error(void);
+
+/* ------------------------------------------------------------------ encoder */
+
+/*
+ * Host-buffer encoder.  Replaces InitSparseMatrixA_bitmap
+ * (csrc/SpMM_API.cuh:112-241) for the tile shape all of its callers pass
+ * (8,16,64,8,64,64; csrc/SpMM_API.cuh:275).  A_h is a host pointer to M*K fp16
+ * values; the work is done on the current CUDA device.  On success the five
+ * output arrays are malloc()ed and owned by the caller (free() or
+ * spb_free_host), exactly like the reference, and bit-identical to it:
+ *   vals      gtile[G] halves (packed non-zeros, each 64x64 tile padded with
+ *             +0.0 to a multiple of 8)
+ *   tile_nnz  M*K/64 ints (non-zeros per 8x8 tile; the reference's "TileOffsets")
+ *   mtile     4*G ints written; allocated M*K/64 ints like the reference (csrc/SpMM_API.cuh:137)
+ *   gtile     G+1 ints
+ *   bitmap    M*K/64 uint64
+ *   max_nnz   largest padded 64x64-tile count (not rounded to 64)
+ * Returns G = (M/64)*(K/64), or -1 when an allocation fails (reference
+ * behaviour), or -(1000+cudaError) when a CUDA call fails.
+ */
+int spb_encode_host(const uint16_t* A_h, int M, int K, uint16_t** vals, int** tile_nnz, int** mtile, int** gtile,
+                    uint64_t** bitmap, int* max_nnz);
+
+void spb_free_host(void* p);
+
+/*
+ * Device-buffer encoder (no reference counterpart: the reference encodes on the
+ * CPU only; csrc/SpMM_API.cuh:112).  All pointers are device pointers.
+ * Asynchronous on `stream`.  vals_capacity is the room at vals_d in halves;
+ * M*K + 8*G always suffices.  After completion gtile_d[G] holds the number of
+ * halves written and *max_nnz_d the largest padded tile count.  If the values
+ * do not fit, nothing is written past the capacity and *status_d (optional,
+ * may be NULL) is set to 1.  scratch_d needs spb_encode_scratch_bytes(M,K).
+ */
+size_t spb_encode_scratch_bytes(int M, int K);
+int spb_encode_device(void* stream, const uint16_t* A_d, int M, int K, uint16_t* vals_d, size_t vals_capacity,
+                      int* tile_nnz_d, int* mtile_d, int* gtile_d, uint64_t* bitmap_d, int* max_nnz_d,
+                      void* scratch_d, int* status_d);
+
+/*
+ * File-level encoder, same name, arguments, output files and failure
+ * behaviour (message + exit(-1)) as the reference's
+ * Our_GenSparseMatrixBinFile (csrc/SpMM_API.cuh:243-320): reads M*K halves,
+ * encodes, rounds max_nnz up to a multiple of 64 and writes the six files.
+ * spb_gen_bin_files is the same but returns non-zero instead of exiting.
+ */
+void Our_GenSparseMatrixBinFile(char* DenseMatrixFileName, int M, int K, char* Compressed_ValFileName,
+                                char* bitmap_TileOffsets_globalFileName, char* bitmap_TileOffsets_medianFileName,
+                                char* bitmapFileName, char* max_nnz_intileFileName, char* OutputSizesFileName);
+int spb_gen_bin_files(const char* dense, int M, int K, const char* val, const char* gtile, const char* mtile,
+                      const char* bitmap, const char* max_nnz, const char* sizes);
+
+/* --------------------------------------------------------------------- SpMM */
+
+/*
+ * C = A_sparse * B.  Replaces SpMM_SplitK_API_bitmap_v3 (csrc/SpMM_API.cuh:47-110;
+ * the 14-argument dense-B form that FasterTransformer's patched wrapper calls,
+ * third_party/ft_spinfer.patch:3736-3749).  Argument order and meaning are the
+ * reference's: A is ignored (may be NULL); Compressed_A, TileOffsets (global
+ * tile offsets), TileOffsets_Median, bitmap, max_nnz_intile (device pointer to
+ * one int), B, C and Reduction_Workspace are device pointers.  With Split_K > 1
+ * the k-tiles are cut into Split_K ranges exactly as the reference does
+ * (csrc/SpMM_Kernel.cuh:35-43), fp16 partials go to Reduction_Workspace
+ * ([Split_K][N][M], at least Split_K*M*N halves) and are summed in fp32 in range
+ * order (csrc/Reduction_Kernel.cuh:24-44).  Asynchronous on `stream`; allocates
+ * nothing on the device.
+ * N may be any positive value (the reference accepts only 8,16,32,64 and
+ * multiples of 128; csrc/SpMM_API.cuh:60-96).  Returns a cudaError_t value;
+ * invalid shapes give cudaErrorInvalidValue and launch nothing.
+ */
+int spb_spmm_bitmap_v3(void* stream, const uint16_t* A, const uint16_t* Compressed_A, const int* TileOffsets,
+                       const int* TileOffsets_Median, const uint64_t* bitmap, const int* max_nnz_intile,
+                       const uint16_t* B, uint16_t* C, int M_Global, int N_Global, int K_Global,
+                       uint16_t* Reduction_Workspace, int Split_K);
+
+/*
+ * Split-K reduction alone.  Replaces the SplitK_Reduction launch
+ * (csrc/SpMM_API.cuh:106-108, csrc/Reduction_Kernel.cuh:24-44).
+ */
+int spb_splitk_reduce(void* stream, uint16_t* C, const uint16_t* Reduction_Workspace, int M_Global, int N_Global,
+                      int Split_K);
+
+/*
+ * Split_K this library would pick for a shape on the current device (the
+ * reference keeps a per-M table in its converter,
+ * end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:23).
+ */
+int spb_suggest_split_k(int M, int N, int K);
+
+/*
+ * Status word of the current device: 0 when no kernel of this library has hit a
+ * bounded wait that ran out or an inconsistent offset since the last reset.
+ * Synchronises the device.  spb_reset_device_status clears it.
+ */
+int spb_device_status(int* status_out);
+int spb_reset_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPMM_B200_H */

@@ -1,0 +1,63 @@
+"""Loader for libSpMM_API.so (the C ABI declared in include/spmm_b200.h).
+
+The library is built in-tree by spmspm_b200.build.build(); there is no Python or
+CPU fallback: if the shared object is missing, loading raises.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libSpMM_API.so")
+
+_u16p = ctypes.POINTER(ctypes.c_uint16)
+_i32p = ctypes.POINTER(ctypes.c_int)
+_u64p = ctypes.POINTER(ctypes.c_uint64)
+_vp = ctypes.c_void_p
+
+# name -> (restype, argtypes); every symbol include/spmm_b200.h declares
+SIGNATURES = {
+    "spb_version": (ctypes.c_int, []),
+    "spb_last_error": (ctypes.c_char_p, []),
+    "spb_encode_host": (ctypes.c_int, [_vp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_u16p), ctypes.POINTER(_i32p),
+                                       ctypes.POINTER(_i32p), ctypes.POINTER(_i32p), ctypes.POINTER(_u64p), _i32p]),
+    "spb_free_host": (None, [_vp]),
+    "spb_encode_scratch_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.c_int]),
+    "spb_encode_device": (ctypes.c_int, [_vp, _vp, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_size_t, _vp, _vp, _vp,
+                                         _vp, _vp, _vp, _vp]),
+    "Our_GenSparseMatrixBinFile": (None, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_char_p] * 6),
+    "spb_gen_bin_files": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_char_p] * 6),
+    "spb_spmm_bitmap_v3": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,
+                                          ctypes.c_int, _vp, ctypes.c_int]),
+    "spb_splitk_reduce": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
+    "spb_suggest_split_k": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
+    "spb_device_status": (ctypes.c_int, [_i32p]),
+    "spb_reset_device_status": (ctypes.c_int, []),
+}
+
+# C++-mangled symbols of the reference header (include/SpMM_API.cuh)
+MANGLED = [
+    "_Z25SpMM_SplitK_API_bitmap_v3P11CUstream_stPK6__halfS3_PKiS5_PKmS5_S3_PS1_iiiS8_i",
+    "_Z24InitSparseMatrixA_bitmapP6__halfiiiiiiiiPS0_PPiS3_S3_PPmRi",
+]
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(nvcc, sm_100a). There is no fallback path.")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def last_error():
+    return load().spb_last_error().decode()

@@ -1,0 +1,237 @@
+"""Host-side mirror of the reference's SpMM library interface, over the C ABI.
+
+Names and argument meaning follow the reference (csrc/SpMM_API.cuh):
+  InitSparseMatrixA_bitmap      -> init_sparse_matrix_a_bitmap   (:112)
+  SpMM_SplitK_API_bitmap_v3     -> spmm_splitk_api_bitmap_v3     (:47)
+  Our_GenSparseMatrixBinFile    -> our_gen_sparse_matrix_bin_file (:243)
+PyTorch is used only to hold device memory and streams.
+"""
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+class SpmmError(RuntimeError):
+    pass
+
+
+def _check(code, what):
+    if code != 0:
+        raise SpmmError(f"{what} failed: cudaError {code}: {_lib.last_error()}")
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream_ptr(stream=None):
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+# --------------------------------------------------------------------------- encoder (host)
+
+@dataclass
+class HostEncoded:
+    """Host arrays in the reference's bitmap-v3 format (what InitSparseMatrixA_bitmap returns)."""
+    M: int
+    K: int
+    vals: np.ndarray       # uint16 [val_count]        Compressed_Val
+    tile_nnz: np.ndarray   # int32  [M*K/64]           TileOffsets (per-8x8 counts)
+    mtile: np.ndarray      # int32  [4*G]              TileOffsets_median
+    gtile: np.ndarray      # int32  [G+1]              TileOffsets_global
+    bitmap: np.ndarray     # uint64 [M*K/64]
+    max_nnz: int
+
+    @property
+    def G(self):
+        return (self.M // 64) * (self.K // 64)
+
+
+def init_sparse_matrix_a_bitmap(A_h):
+    """Encode a host fp16 matrix [M,K] on the GPU; returns HostEncoded (bit-identical to the reference)."""
+    A_h = np.ascontiguousarray(A_h)
+    if A_h.dtype == np.float16:
+        A_h = A_h.view(np.uint16)
+    if A_h.dtype != np.uint16 or A_h.ndim != 2:
+        raise SpmmError("A must be a 2-D float16/uint16 array")
+    M, K = A_h.shape
+    lib = _lib.load()
+    u16p, i32p, u64p = ctypes.POINTER(ctypes.c_uint16), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_uint64)
+    vals, tn, mt, gt, bm = u16p(), i32p(), i32p(), i32p(), u64p()
+    mx = ctypes.c_int(0)
+    g = lib.spb_encode_host(ctypes.c_void_p(A_h.ctypes.data), M, K, ctypes.byref(vals), ctypes.byref(tn),
+                            ctypes.byref(mt), ctypes.byref(gt), ctypes.byref(bm), ctypes.byref(mx))
+    try:
+        if g < 0:
+            raise SpmmError(f"InitSparseMatrixA_bitmap failed ({g}): {_lib.last_error()}")
+        nt = M * K // 64
+        gtile = np.ctypeslib.as_array(gt, (g + 1,)).copy()
+        n = int(gtile[g])
+        out = HostEncoded(
+            M, K,
+            np.ctypeslib.as_array(vals, (n,)).copy() if n else np.zeros(0, np.uint16),
+            np.ctypeslib.as_array(tn, (nt,)).copy(),
+            np.ctypeslib.as_array(mt, (4 * g,)).copy(),
+            gtile,
+            np.ctypeslib.as_array(bm, (nt,)).copy(),
+            mx.value)
+    finally:
+        for p in (vals, tn, mt, gt, bm):
+            lib.spb_free_host(ctypes.cast(p, ctypes.c_void_p))
+    return out
+
+
+def our_gen_sparse_matrix_bin_file(dense, M, K, val, gtile, mtile, bitmap, max_nnz, sizes):
+    """Non-exiting form of Our_GenSparseMatrixBinFile: raises on failure."""
+    enc = [s.encode() for s in (dense, val, gtile, mtile, bitmap, max_nnz, sizes)]
+    rc = _lib.load().spb_gen_bin_files(enc[0], M, K, *enc[1:])
+    if rc != 0:
+        raise SpmmError(_lib.last_error())
+
+
+# --------------------------------------------------------------------------- encoder (device)
+
+@dataclass
+class BitmapMatrix:
+    """A weight matrix resident on the GPU in bitmap-v3 form."""
+    M: int
+    K: int
+    vals: torch.Tensor      # float16 [>= val_count]
+    gtile: torch.Tensor     # int32 [G+1]
+    mtile: torch.Tensor     # int32 [4G]
+    bitmap: torch.Tensor    # int64 view of uint64 [M*K/64]
+    max_nnz: torch.Tensor   # int32 [1] (device; the kernel dereferences it)
+    tile_nnz: torch.Tensor = None
+    val_count: int = -1
+
+    @property
+    def G(self):
+        return (self.M // 64) * (self.K // 64)
+
+    def algorithmic_bytes(self, N):
+        """Bytes one SpMM must move: packed values, bitmaps, offsets, activations, output."""
+        G = self.G
+        return 2 * self.val_count + 8 * (self.M * self.K // 64) + 4 * (G + 1) + 16 * G + 2 * self.K * N + 2 * self.M * N
+
+    def shard_rows(self, rank, world):
+        """Rows [rank*M/world, (rank+1)*M/world) as a BitmapMatrix that shares storage where it can.
+
+        Global tiles are ordered row-block-major, so a row shard is a contiguous slice of
+        every array; only the global offsets need re-basing.
+        """
+        if self.M % (64 * world):
+            raise SpmmError("M/world must be a multiple of 64")
+        Ms = self.M // world
+        gk = self.K // 64
+        g0, g1 = rank * (Ms // 64) * gk, (rank + 1) * (Ms // 64) * gk
+        gt_h = self.gtile[[g0, g1]].cpu()
+        o0, o1 = int(gt_h[0]), int(gt_h[1])
+        gtile = (self.gtile[g0:g1 + 1] - o0).contiguous()
+        sizes = gtile[1:] - gtile[:-1]
+        mx = sizes.max().to(torch.int32).reshape(1) if sizes.numel() else torch.zeros(1, dtype=torch.int32, device=self.vals.device)
+        return BitmapMatrix(Ms, self.K, self.vals[o0:o1], gtile, self.mtile[4 * g0:4 * g1],
+                            self.bitmap[64 * g0:64 * g1], mx,
+                            self.tile_nnz[64 * g0:64 * g1] if self.tile_nnz is not None else None, o1 - o0)
+
+
+def encode_device(A, stream=None):
+    """Encode a CUDA fp16 tensor [M,K] on the GPU (spb_encode_device)."""
+    if not (A.is_cuda and A.dtype == torch.float16 and A.dim() == 2 and A.is_contiguous()):
+        raise SpmmError("A must be a contiguous CUDA float16 matrix")
+    M, K = A.shape
+    if M % 64 or K % 64:
+        raise SpmmError("M and K must be multiples of 64")
+    lib = _lib.load()
+    dev = A.device
+    G = (M // 64) * (K // 64)
+    nt = M * K // 64
+    tile_nnz = torch.empty(nt, dtype=torch.int32, device=dev)
+    mtile = torch.empty(4 * G, dtype=torch.int32, device=dev)
+    gtile = torch.empty(G + 1, dtype=torch.int32, device=dev)
+    bitmap = torch.empty(nt, dtype=torch.int64, device=dev)
+    max_nnz = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(lib.spb_encode_scratch_bytes(M, K), dtype=torch.uint8, device=dev)
+    cap = M * K + 8 * G
+    vals = torch.empty(cap, dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib.spb_encode_device(_stream_ptr(stream), _ptr(A), M, K, _ptr(vals), cap, _ptr(tile_nnz), _ptr(mtile),
+                                     _ptr(gtile), _ptr(bitmap), _ptr(max_nnz), _ptr(scratch), _ptr(status)),
+               "spb_encode_device")
+    n = int(gtile[G].item())
+    if int(status.item()) != 0:
+        raise SpmmError("encoder overflowed its value buffer")
+    # release the worst-case buffer (an all-zero matrix keeps 16 bytes so the pointer is never null)
+    vals = vals[:n].clone() if n else torch.zeros(8, dtype=torch.float16, device=dev)
+    return BitmapMatrix(M, K, vals, gtile, mtile, bitmap, max_nnz, tile_nnz, n)
+
+
+def to_device(enc: HostEncoded, device="cuda"):
+    """Upload reference-format host arrays (what the FT loader does with the .bin files)."""
+    dev = torch.device(device)
+    mx = enc.max_nnz
+    return BitmapMatrix(
+        enc.M, enc.K,
+        torch.from_numpy(enc.vals.view(np.float16).copy()).to(dev) if enc.vals.size else torch.zeros(8, dtype=torch.float16, device=dev),
+        torch.from_numpy(enc.gtile.copy()).to(dev),
+        torch.from_numpy(enc.mtile.copy()).to(dev),
+        torch.from_numpy(enc.bitmap.view(np.int64).copy()).to(dev),
+        torch.tensor([mx], dtype=torch.int32, device=dev),
+        torch.from_numpy(enc.tile_nnz.copy()).to(dev),
+        int(enc.vals.size))
+
+
+# --------------------------------------------------------------------------- SpMM
+
+def spmm_splitk_api_bitmap_v3(stream, A, Compressed_A, TileOffsets, TileOffsets_Median, bitmap, max_nnz_intile, B, C,
+                              M_Global, N_Global, K_Global, Reduction_Workspace, Split_K):
+    """Same argument list as the reference's SpMM_SplitK_API_bitmap_v3 (csrc/SpMM_API.cuh:47); tensors for pointers.
+
+    A is ignored (FasterTransformer passes nullptr).  Raises SpmmError with the CUDA error code on failure.
+    """
+    lib = _lib.load()
+    code = lib.spb_spmm_bitmap_v3(_stream_ptr(stream), _ptr(A), _ptr(Compressed_A), _ptr(TileOffsets),
+                                  _ptr(TileOffsets_Median), _ptr(bitmap), _ptr(max_nnz_intile), _ptr(B), _ptr(C),
+                                  M_Global, N_Global, K_Global, _ptr(Reduction_Workspace), Split_K)
+    _check(code, "SpMM_SplitK_API_bitmap_v3")
+
+
+def suggest_split_k(M, N, K):
+    return _lib.load().spb_suggest_split_k(M, N, K)
+
+
+def spmm(W: BitmapMatrix, B, split_k=None, out=None, workspace=None, stream=None):
+    """C[N,M] = (W @ B^T)^T with B given as [N,K] (the reference's column-major K x N)."""
+    if not (B.is_cuda and B.dtype == torch.float16 and B.dim() == 2 and B.is_contiguous() and B.shape[1] == W.K):
+        raise SpmmError("B must be a contiguous CUDA float16 [N,K] tensor")
+    N = B.shape[0]
+    if split_k is None:
+        split_k = suggest_split_k(W.M, N, W.K)
+    if out is None:
+        out = torch.empty((N, W.M), dtype=torch.float16, device=B.device)
+    if split_k > 1 and workspace is None:
+        workspace = torch.empty(split_k * N * W.M, dtype=torch.float16, device=B.device)
+    with torch.cuda.device(B.device):
+        spmm_splitk_api_bitmap_v3(stream, None, W.vals, W.gtile, W.mtile, W.bitmap, W.max_nnz, B, out, W.M, N, W.K,
+                                  workspace, split_k)
+    return out
+
+
+def splitk_reduce(C, workspace, M, N, split_k, stream=None):
+    _check(_lib.load().spb_splitk_reduce(_stream_ptr(stream), _ptr(C), _ptr(workspace), M, N, split_k),
+           "spb_splitk_reduce")
+
+
+def device_status():
+    st = ctypes.c_int(0)
+    _check(_lib.load().spb_device_status(ctypes.byref(st)), "spb_device_status")
+    return st.value
+
+
+def reset_device_status():
+    _check(_lib.load().spb_reset_device_status(), "spb_reset_device_status")
