@@ -1,0 +1,67 @@
+"""The C-ABI library loads and exports every symbol include/spmm_b200.h and include/SpMM_API.cuh declare.
+
+No compute entry point is called here (no GPU in this tier of the suite).
+"""
+import ctypes
+import os
+import re
+import subprocess
+
+from conftest import ROOT
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "spmm_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(spb_\w+|Our_GenSparseMatrixBinFile)\s*\(", text)))
+
+
+def test_header_declares_expected_entry_points():
+    names = _declared_functions()
+    for n in ("spb_encode_host", "spb_encode_device", "spb_spmm_bitmap_v3", "spb_splitk_reduce",
+              "Our_GenSparseMatrixBinFile"):
+        assert n in names
+
+
+def test_library_exports_every_declared_symbol(lib_built):
+    from spmspm_b200 import _lib
+    for name in _declared_functions():
+        assert hasattr(lib_built, name), name
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    for name in _lib.SIGNATURES:
+        assert name in _declared_functions(), f"{name} bound but not declared in the header"
+
+
+def test_library_exports_reference_mangled_symbols(lib_built):
+    from spmspm_b200 import _lib
+    for sym in _lib.MANGLED:
+        ctypes.cast(getattr(lib_built, sym), ctypes.c_void_p)
+
+
+def test_version_and_error_string(lib_built):
+    assert lib_built.spb_version() >= 100
+    assert isinstance(lib_built.spb_last_error(), bytes)
+
+
+def test_reference_header_compiles_against_the_library(tmp_path, lib_built):
+    """A translation unit written like the reference's callers compiles and links unchanged."""
+    src = tmp_path / "caller.cu"
+    src.write_text(r'''
+#include "SpMM_API.cuh"
+int main(int argc, char**) {
+    if (argc > 100) {  // never executed: link check only
+        half* v; int *a, *b, *c; uint64_t* bm; int mx;
+        InitSparseMatrixA_bitmap(nullptr, 64, 64, 8, 16, 64, 8, 64, 64, &v, &a, &b, &c, &bm, mx);
+        SpMM_SplitK_API_bitmap_v3(0, nullptr, v, c, b, bm, a, v, v, 64, 16, 64, v, 1);
+        Our_GenSparseMatrixBinFile(nullptr, 64, 64, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+    }
+    return 0;
+}
+''')
+    exe = tmp_path / "caller"
+    libdir = os.path.join(ROOT, "spmspm_b200")
+    r = subprocess.run(["/usr/local/cuda/bin/nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
+                        "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe), "-L", libdir,
+                        "-l:libSpMM_API.so", "-Xlinker", f"-rpath={libdir}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert subprocess.run([str(exe)]).returncode == 0

@@ -1,0 +1,172 @@
+"""SpMM parity through the C ABI: CUDA kernel vs the CPU oracle on the same seeded inputs.
+
+Tolerance (fp16 output, fp32 accumulation): max |c - ref| <= 1e-2 * max|ref| and element-wise
+|c - ref| <= 1e-2 * |ref| + 1e-2 * rms(ref), ref = fp32 host GEMM.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+import oracle  # noqa: E402
+from conftest import make_dense, make_sparse  # noqa: E402
+
+REL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def sp(lib_built):
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import spmspm_b200
+    spmspm_b200.reset_device_status()
+    return spmspm_b200
+
+
+def _assert_close(C, ref):
+    C = C.astype(np.float32)
+    scale = max(float(np.abs(ref).max()), 1e-12)
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    err = np.abs(C - ref)
+    assert float(err.max()) <= REL * scale, f"max err {err.max()} vs scale {scale}"
+    assert np.all(err <= REL * np.abs(ref) + REL * rms + 1e-12)
+
+
+def _run(sp, A, B, split_k):
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    C = sp.spmm(W, torch.from_numpy(B).cuda(), split_k=split_k)
+    torch.cuda.synchronize()
+    return C.cpu().numpy()
+
+
+@pytest.mark.parametrize("M,K,N,s,sk", [
+    (64, 64, 16, 0.5, 1),        # smallest legal shape: half-filled 128-row block
+    (128, 64, 8, 0.5, 1),        # N = 8 (padded activation tile)
+    (128, 128, 16, 0.5, 2),
+    (192, 512, 16, 0.6, 1),      # odd number of 64-row tiles
+    (256, 512, 32, 0.6, 3),      # split-K not dividing the 8 k-tiles
+    (1024, 1024, 64, 0.4, 4),
+    (512, 1024, 128, 0.5, 1),
+    (512, 1024, 256, 0.5, 2),    # two activation tiles
+    (512, 1024, 24, 0.7, 1),     # N the reference rejects
+    (256, 2048, 1, 0.6, 1),
+    (128, 4096, 16, 0.0, 1),     # fully dense tiles (4096 values per global tile)
+    (128, 4096, 16, 1.0, 1),     # all-zero matrix
+    (4096, 4096, 16, 0.5, 1),    # BASELINE config 1
+    (4096, 4096, 16, 0.5, 6),
+    (5120, 5120, 16, 0.6, 6),    # OPT-13B out-proj
+    (5120, 20480, 8, 0.6, 8),    # OPT-13B FC2
+])
+def test_spmm_matches_fp32_oracle(sp, M, K, N, s, sk):
+    A = make_sparse(M, K, s, seed=M + 3 * K + N)
+    B = make_dense(N, K, seed=N + K, dist="uniform" if M == 4096 else "normal")
+    C = _run(sp, A, B, sk)
+    _assert_close(C, oracle.gemm_f32(A, B))
+    assert sp.device_status() == 0
+
+
+def test_spmm_from_reference_format_host_arrays(sp):
+    """Arrays produced by the reference-format host encoder, uploaded as FT's loader would, max_nnz rounded to 64."""
+    A = make_sparse(384, 640, 0.6, seed=77)
+    B = make_dense(16, 640, seed=78)
+    h = sp.init_sparse_matrix_a_bitmap(A)
+    if h.max_nnz % 64:
+        h.max_nnz = (h.max_nnz // 64 + 1) * 64   # reference csrc/SpMM_API.cuh:284-286
+    W = sp.to_device(h)
+    C = sp.spmm(W, torch.from_numpy(B).cuda(), split_k=2)
+    torch.cuda.synchronize()
+    _assert_close(C.cpu().numpy(), oracle.gemm_f32(A, B))
+
+
+def test_split_k_chain_close_to_reference_rounding(sp):
+    """Same split ranges and rounding points as the reference; accumulation order inside a range may differ."""
+    A = make_sparse(256, 2048, 0.5, seed=5)
+    B = make_dense(16, 2048, seed=6)
+    for sk in (2, 5):
+        C = _run(sp, A, B, sk).astype(np.float32)
+        want = oracle.spmm_splitk_f16(A, B, sk).view(np.float16).astype(np.float32)
+        assert np.abs(C - want).max() <= 4e-3 * np.abs(want).max()
+
+
+def test_reduction_kernel_bit_exact(sp):
+    rng = np.random.default_rng(4)
+    M, N, sk = 256, 24, 7
+    parts = rng.standard_normal((sk, N, M)).astype(np.float16)
+    ws = torch.from_numpy(parts).cuda()
+    C = torch.empty((N, M), dtype=torch.float16, device="cuda")
+    sp.splitk_reduce(C, ws, M, N, sk)
+    torch.cuda.synchronize()
+    assert np.array_equal(C.cpu().numpy().view(np.uint16), oracle.splitk_reduce(parts, M, N, sk))
+
+
+def test_special_values_propagate(sp):
+    """inf in the weights reaches the output; NaN payloads are kept by the encoder and poison only their row."""
+    A = make_sparse(128, 256, 0.5, seed=8)
+    A[3, 10] = np.float16(np.inf)
+    A[70, 200] = np.float16(np.nan)
+    B = np.abs(make_dense(16, 256, seed=9)) + np.float16(0.5)
+    C = _run(sp, A, B, 1).astype(np.float32)
+    assert np.all(np.isinf(C[:, 3])) and np.all(np.isnan(C[:, 70]))
+    ok_rows = [r for r in range(128) if r not in (3, 70)]
+    ref = oracle.gemm_f32(A, B)
+    assert np.abs(C[:, ok_rows] - ref[:, ok_rows]).max() <= REL * np.abs(ref[:, ok_rows]).max()
+
+
+def test_linearity_at_full_size(sp):
+    """OPT-30B FC1 shape (28672 x 7168, 60 %): S(B1 + B2) == S(B1) + S(B2) within fp16 rounding, and the result
+    matches an fp32 product of the decoded weight on sampled rows."""
+    M, K, N = 28672, 7168, 16
+    g = torch.Generator(device="cuda").manual_seed(0x5EED0002)
+    A = (torch.randn((M, K), device="cuda", generator=g) * 0.02).half()
+    A[torch.rand((M, K), device="cuda", generator=g) < 0.6] = 0
+    W = sp.encode_device(A)
+    B1 = torch.randn((N, K), device="cuda", generator=g).half()
+    B2 = torch.randn((N, K), device="cuda", generator=g).half()
+    Bs = (B1.float() + B2.float()).half()
+    C1 = sp.spmm(W, B1, split_k=1).float()
+    C2 = sp.spmm(W, B2, split_k=1).float()
+    Cs = sp.spmm(W, Bs, split_k=2).float()
+    scale = float(Cs.abs().max())
+    assert float((Cs - (C1 + C2)).abs().max()) <= 1e-2 * scale
+    rows = torch.randint(0, M, (512,), device="cuda", generator=g)
+    ref = Bs.float() @ A[rows].float().T
+    assert float((Cs[:, rows] - ref).abs().max()) <= REL * float(ref.abs().max())
+    # CPU oracle on a 256-row slab of the same matrix
+    slab = A[1024:1280].cpu().numpy()
+    want = oracle.gemm_f32(slab, Bs.cpu().numpy())
+    assert np.abs(Cs[:, 1024:1280].cpu().numpy() - want).max() <= REL * np.abs(want).max()
+    assert sp.device_status() == 0
+
+
+def test_errors_launch_nothing(sp):
+    A = make_sparse(128, 128, 0.5, seed=1)
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    B = torch.zeros((16, 128), dtype=torch.float16, device="cuda")
+    C = torch.full((16, 128), 7.0, dtype=torch.float16, device="cuda")
+    with pytest.raises(sp.SpmmError):   # M not a multiple of 64
+        sp.spmm_splitk_api_bitmap_v3(None, None, W.vals, W.gtile, W.mtile, W.bitmap, W.max_nnz, B, C, 100, 16, 128, None, 1)
+    with pytest.raises(sp.SpmmError):   # split-K without a workspace
+        sp.spmm_splitk_api_bitmap_v3(None, None, W.vals, W.gtile, W.mtile, W.bitmap, W.max_nnz, B, C, 128, 16, 128, None, 2)
+    with pytest.raises(sp.SpmmError):   # more ranges than k-tiles
+        sp.spmm(W, B, split_k=3)
+    with pytest.raises(sp.SpmmError):   # misaligned activation pointer
+        Bm = torch.zeros(16 * 128 + 8, dtype=torch.float16, device="cuda")[1:16 * 128 + 1].view(16, 128)
+        sp.spmm_splitk_api_bitmap_v3(None, None, W.vals, W.gtile, W.mtile, W.bitmap, W.max_nnz, Bm, C, 128, 16, 128, None, 1)
+    torch.cuda.synchronize()
+    assert float(C.min()) == 7.0 and float(C.max()) == 7.0
+
+
+def test_stream_and_repeat_calls(sp):
+    A = make_sparse(512, 1024, 0.6, seed=2)
+    B = make_dense(16, 1024, seed=3)
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    Bd = torch.from_numpy(B).cuda()
+    ref = oracle.gemm_f32(A, B)
+    s = torch.cuda.Stream()
+    outs = []
+    with torch.cuda.stream(s):
+        for sk in (1, 2, 4, 1, 2):
+            outs.append(sp.spmm(W, Bd, split_k=sk, stream=s))
+    s.synchronize()
+    for C in outs:
+        _assert_close(C.cpu().numpy(), ref)
