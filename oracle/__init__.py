@@ -149,6 +149,17 @@ def gemm_f32(A, B):
     return C
 
 
+def spmm_f32(enc, B):
+    """fp32 product straight from the compressed form (decode + GEMM) -> C [N,M] float32."""
+    B = _as_u16(B)
+    N = B.shape[0]
+    C = np.empty((N, enc.M), np.float32)
+    vals = enc.vals if enc.vals.size else np.zeros(1, np.uint16)
+    lib().oracle_spmm_f32(_p(vals, _u16p), _p(enc.mtile, _i32p), _p(enc.gtile, _i32p), _p(enc.bitmap, _u64p),
+                          _p(B, _u16p), _p(C, _f32p), enc.M, N, enc.K)
+    return C
+
+
 def spmm_splitk_f16(A, B, split_k):
     """The reference's split-K rounding chain on a dense copy of A -> C [N,M] uint16 (fp16 bits)."""
     A, B = _as_u16(A), _as_u16(B)

@@ -187,6 +187,7 @@ void oracle_decode_bitmap_v3(const uint16_t *vals, const int *mtile, const int *
                              const uint64_t *bitmap, int M, int K, uint16_t *A_out)
 {
     int GM = M / 64, GK = K / 64;
+#pragma omp parallel for schedule(static)
     for (int gm = 0; gm < GM; ++gm)
         for (int gk = 0; gk < GK; ++gk) {
             int g = gm * GK + gk;
