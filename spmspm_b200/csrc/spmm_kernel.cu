@@ -7,9 +7,10 @@
 //                   offsets of two vertically adjacent 64x64 global tiles) with
 //                   1-D bulk copies and the activation tile with a 2-D TMA load into a
 //                   ring of shared-memory stages, completion on mbarriers;
-//   decode warps    (2 groups x 4 warps, one thread per weight row) expand the bitmaps:
+//   decode warps    (groups of 4 warps, one thread per weight row) expand the bitmaps:
 //                   a first pass turns the 128 tile bitmaps of the stage into per-row
-//                   value offsets with popcount + a 16-lane prefix sum, a second pass
+//                   value offsets with byte-wise popcounts + a 16-lane prefix sum, a second
+//                   pass
 //                   gathers each row's values and writes the dense 128 x 64 fp16 tile
 //                   straight into tensor memory (tcgen05.st) as the MMA's A operand;
 //   MMA warp        one thread issues tcgen05.mma (M=128, N=16..128, K=16, fp16 in,
@@ -30,16 +31,26 @@
 namespace spb {
 namespace {
 
-constexpr int kThreads = 448;         // 14 warps
+#ifndef SPB_DECODE_GROUPS
+#define SPB_DECODE_GROUPS 3
+#endif
+constexpr int kDecodeGroups = SPB_DECODE_GROUPS;  // each group: 4 warps, one thread per weight row
 constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 2;     // warps 2..5
-constexpr int kDecodeWarp0 = 6;       // warps 6..13
-constexpr int kDecodeGroups = 2;
-constexpr int kABufs = 4;             // A-operand buffers in TMEM (32 columns each)
+constexpr int kDecodeWarp0 = 6;       // warps 6..
+constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kDecodeGroups);
+constexpr int kABufs = 2 * kDecodeGroups;  // A-operand buffers in TMEM (32 columns each)
 constexpr int kMaxStages = 24;
-constexpr int kMetaBytes = kDecodeGroups * 2 * 128 * 16;
+// Per-row metadata of one stage: word = value offset (16 bit) | row mask << 16 | row count << 24.
+// Rows 0-3 and rows 4-7 of a tile live in two regions whose distance is 16 mod 32 words and every
+// 16-tile median group is shifted by 8 words, so that the 32 rows a warp reads at once fall into
+// 32 different banks.
+constexpr int kMetaRegionWords = 592;
+constexpr int kMetaBufBytes = 2 * kMetaRegionWords * 4;
+constexpr int kMetaBytes = ((kDecodeGroups * 2 * kMetaBufBytes + 1023) / 1024) * 1024;
 constexpr int kHeaderBytes = 1024;
+constexpr int kLutOffset = 640;       // two 16-entry selector tables inside the header
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct KernelParams {
@@ -204,18 +215,86 @@ __device__ __forceinline__ Item decode_item(const KernelParams& p, int item)
     return it;
 }
 
-// Expand one 8-element row segment: `mask` bit c set <=> element c is the next packed value.
-__device__ __forceinline__ void expand_row(const uint16_t* __restrict__ v, uint32_t mask, uint32_t (&out)[4])
+__device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t* r)
 {
-    uint32_t h[8];
-    int idx = 0;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        h[c] = 0;
-        if (mask & (1u << c)) h[c] = v[idx++];
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) out[j] = h[2 * j] | (h[2 * j + 1] << 16);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
+            taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// prmt.b32 in its default mode: selector nibble bits 2:0 pick one of the 8 source bytes, bit 3
+// replaces the byte by 8 copies of its sign bit.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void lds32x3(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c)
+{
+    asm volatile("ld.shared.b32 %0, [%3];\n\tld.shared.b32 %1, [%3+4];\n\tld.shared.b32 %2, [%3+8];"
+                 : "=&r"(a), "=&r"(b), "=&r"(c)
+                 : "r"(addr));
+}
+
+// Selector tables for expanding a row segment with byte permutes.  A row's 8-bit mask is split in
+// two nibbles.  The low nibble's (up to 4) values are the first values of the row, the high
+// nibble's the last, so the low half is expanded from a window starting at the row's first value
+// and the high half from a window ending at its last value.
+//   low  entry: sel(pos 0,1 from {v0,v1 | zero})  |  sel(pos 2,3 from {v0..v3}) << 16
+//   high entry: sel(pos 4,5 from {v[k-4..k-1]})   |  sel(pos 6,7 from {v[k-2],v[k-1] | zero}) << 16
+__device__ __forceinline__ uint32_t lut_low_entry(uint32_t n)
+{
+    const uint32_t b0 = n & 1, b1 = (n >> 1) & 1, b2 = (n >> 2) & 1;
+    const uint32_t p0 = b0 ? 0x10u : 0x54u;
+    const uint32_t p1 = b1 ? (b0 ? 0x32u : 0x10u) : 0x54u;
+    const uint32_t i2 = b0 + b1, i3 = i2 + b2;
+    const uint32_t s1 = (0x10u + 0x22u * i2) | ((0x10u + 0x22u * i3) << 8);
+    return (p0 | (p1 << 8)) | (s1 << 16);
+}
+__device__ __forceinline__ uint32_t lut_high_entry(uint32_t n)
+{
+    const uint32_t b5 = (n >> 1) & 1, b6 = (n >> 2) & 1, b7 = (n >> 3) & 1;
+    const uint32_t h4 = 3 - (b5 + b6 + b7), h5 = 3 - (b6 + b7);
+    const uint32_t s2 = (0x10u + 0x22u * h4) | ((0x10u + 0x22u * h5) << 8);
+    const uint32_t p6 = b6 ? (b7 ? 0x10u : 0x32u) : 0x54u;
+    const uint32_t p7 = b7 ? 0x32u : 0x54u;
+    return s2 | ((p6 | (p7 << 8)) << 16);
+}
+
+// Expand one 8-element row segment described by `meta` (see kMetaRegionWords) into 4 registers
+// of packed fp16.  vbase: shared address of the stage's value region; lut: shared address of the
+// selector tables.
+__device__ __forceinline__ void decode_unit(uint32_t meta, uint32_t vbase, uint32_t lut, uint32_t* o)
+{
+    const uint32_t off2 = (meta << 1) & 0x1fffeu;  // byte offset of the row's first value
+    const uint32_t k2 = (meta >> 23) & 0x1eu;      // 2 * number of values in the row
+    const uint32_t mask = (meta >> 16) & 0xffu;
+    uint32_t x0, x1, x2, y0, y1, y2;
+    lds32x3(vbase + (off2 & ~3u), x0, x1, x2);
+    const uint32_t ot2 = off2 + k2 - 8u;           // byte offset of the value 4 before the row's end
+    lds32x3(vbase + (ot2 & ~3u), y0, y1, y2);
+    const uint32_t L = lds32(lut + ((mask & 15u) << 2));
+    const uint32_t H = lds32(lut + 64u + ((mask >> 4) << 2));
+    const uint32_t selb = 0x3210u + ((off2 >> 1) & 1u) * 0x2222u;
+    const uint32_t selt = 0x3210u + ((ot2 >> 1) & 1u) * 0x2222u;
+    const uint32_t b0 = prmt(x0, x1, selb), b1 = prmt(x1, x2, selb);
+    const uint32_t t0 = prmt(y0, y1, selt), t1 = prmt(y1, y2, selt);
+    // 0xffff per kept position: mask bit -> sign bit of a byte -> replicated by the permute
+    const uint32_t z1 = (mask & 0x0cu) * 0x1020u, z2 = (mask & 0x30u) * 0x0408u;
+    const uint32_t k1 = prmt(z1, z1, 0x9988u), k2m = prmt(z2, z2, 0x9988u);
+    o[0] = prmt(b0, 0u, L);
+    o[1] = prmt(b0, b1, L >> 16) & k1;
+    o[2] = prmt(t0, t1, H) & k2m;
+    o[3] = prmt(t1, 0u, H >> 16);
 }
 
 template <int NPAD>
@@ -270,6 +349,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x >= 32 && threadIdx.x < 64) {
+        uint32_t* lut = reinterpret_cast<uint32_t*>(smem + kLutOffset);
+        const uint32_t n = threadIdx.x - 32;
+        lut[n] = n < 16 ? lut_low_entry(n) : lut_high_entry(n - 16);
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
@@ -418,16 +502,21 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
     } else {
         // ================================================================= decode
-        const int dw = warp - kDecodeWarp0;    // 0..7
-        const int group = dw >> 2;             // 0..1
+        const int dw = warp - kDecodeWarp0;
+        const int group = dw >> 2;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;      // weight row inside the 128-row block == tile index in pass 1
         const int bar_id = 1 + group;
-        uint8_t* meta_g = meta_base + group * (2 * 128 * 16);
-        // pass-2 constants: the 8 tiles of this row are tbase + 2q, q = 0..7
+        uint8_t* meta_g = meta_base + group * (2 * kMetaBufBytes);
+        const uint32_t lut = smem_u32(smem + kLutOffset);
+        // pass 1: this thread owns tile `row` of the stage (tile t of chunk t>>6)
         const int chunk = row >> 6, rr = row & 63;
+        const uint32_t p1_word = (uint32_t)row * 4 + 8 * (uint32_t)(row >> 4);
+        // pass 2: the 8 tiles crossing this weight row are tbase + 2q, q = 0..7
         const int tbase = chunk * 64 + 16 * (rr >> 4) + ((rr >> 3) & 1);
         const int r_in_tile = rr & 7;
+        const uint32_t p2_word = (uint32_t)(r_in_tile >> 2) * kMetaRegionWords + (uint32_t)tbase * 4 +
+                                 (uint32_t)(r_in_tile & 3) + 8 * (uint32_t)(tbase >> 4);
 
         uint32_t it = 0, mine = 0;
         bool ok = true;
@@ -439,63 +528,67 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 if ((int)(it % kDecodeGroups) != group) continue;
                 const uint32_t slot = it % (uint32_t)S, round = it / (uint32_t)S;
                 const uint32_t abuf = it % kABufs, around = it / kABufs;
-                bool got = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
+                const bool got = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
                 const uint8_t* st = stage_base + (size_t)slot * stage_bytes;
-                const uint64_t* bm_s = reinterpret_cast<const uint64_t*>(st + off_bm);
-                const int* mt_s = reinterpret_cast<const int*>(st + off_mt);
-                const uint16_t* val_s = reinterpret_cast<const uint16_t*>(st + off_v0);
-                uint8_t* meta = meta_g + (mine & 1) * (128 * 16);
+                uint32_t* meta = reinterpret_cast<uint32_t*>(meta_g + (mine & 1) * kMetaBufBytes);
                 ++mine;
-                // ---- pass 1: thread <-> tile `row`; per-row value offsets of that tile
+                // ---- pass 1: per-row value offsets, masks and counts of tile `row`
                 {
-                    const uint64_t bm = (got && valid) ? bm_s[row] : 0ull;
-                    const int cnt = __popcll(bm);
-                    int x = cnt;
+                    uint2 bm = make_uint2(0u, 0u);
+                    int mt = 0;
+                    if (got && valid) {
+                        bm = reinterpret_cast<const uint2*>(st + off_bm)[row];
+                        mt = reinterpret_cast<const int*>(st + off_mt)[chunk * 4 + (rr >> 4)];
+                    }
+                    // per-byte population counts (one byte of the bitmap = one tile row)
+                    uint32_t a = bm.x - ((bm.x >> 1) & 0x55555555u);
+                    a = (a & 0x33333333u) + ((a >> 2) & 0x33333333u);
+                    a = (a + (a >> 4)) & 0x0f0f0f0fu;
+                    uint32_t b = bm.y - ((bm.y >> 1) & 0x55555555u);
+                    b = (b & 0x33333333u) + ((b >> 2) & 0x33333333u);
+                    b = (b + (b >> 4)) & 0x0f0f0f0fu;
+                    const uint32_t ia = a * 0x01010101u, ib = b * 0x01010101u;  // inclusive byte prefixes
+                    const uint32_t tl = ia >> 24;
+                    const int cnt = (int)(tl + (ib >> 24));
+                    int x = cnt;                                               // 16-lane scan: tiles of a median tile
 #pragma unroll
                     for (int d = 1; d < 16; d <<= 1) {
                         const int y = __shfl_up_sync(0xffffffffu, x, d, 16);
                         if ((lane & 15) >= d) x += y;
                     }
-                    const int mt = (got && valid) ? mt_s[chunk * 4 + (rr >> 4)] : 0;
                     const uint32_t base = (uint32_t)chunk * (vmax >> 1) + (uint32_t)mt + (uint32_t)(x - cnt);
-                    uint32_t o[8];
+                    const uint32_t base_hi = base + tl;
+                    const uint32_t ea = ia << 8, eb = ib << 8;                   // exclusive prefixes, byte 0 == 0
+                    uint4 lo4, hi4;
+                    uint32_t* lo_w = reinterpret_cast<uint32_t*>(&lo4);
+                    uint32_t* hi_w = reinterpret_cast<uint32_t*>(&hi4);
 #pragma unroll
-                    for (int r = 0; r < 8; ++r)
-                        o[r] = base + (uint32_t)__popcll(bm & ((1ull << (8 * r)) - 1ull));
-                    uint4 pk;
-                    pk.x = (o[0] & 0xffffu) | (o[1] << 16);
-                    pk.y = (o[2] & 0xffffu) | (o[3] << 16);
-                    pk.z = (o[4] & 0xffffu) | (o[5] << 16);
-                    pk.w = (o[6] & 0xffffu) | (o[7] << 16);
-                    reinterpret_cast<uint4*>(meta)[row] = pk;
+                    for (int r = 0; r < 4; ++r) {
+                        const uint32_t s1 = (uint32_t)r | ((uint32_t)(4 + r) << 4);
+                        const uint32_t s2 = (uint32_t)r | (4u << 8) | (5u << 12);
+                        lo_w[r] = prmt(ea, prmt(bm.x, a, s1), s2) + base;
+                        hi_w[r] = prmt(eb, prmt(bm.y, b, s1), s2) + base_hi;
+                    }
+                    *reinterpret_cast<uint4*>(meta + p1_word) = lo4;
+                    *reinterpret_cast<uint4*>(meta + kMetaRegionWords + p1_word) = hi4;
                 }
                 ok = bar_and(bar_id, 128, got && !*abort_flag);
                 if (!ok) break;
-                // ---- pass 2: thread <-> weight row; gather its 64 values
+                // ---- pass 2: thread <-> weight row; gather its 64 values, 8 per tile
+                const uint32_t vbase = smem_u32(st + off_v0);
+                const uint32_t maddr = smem_u32(meta + p2_word);
                 uint32_t a[32];
-                {
-                    const uint16_t* meta16 = reinterpret_cast<const uint16_t*>(meta);
-                    const uint8_t* bm_bytes = reinterpret_cast<const uint8_t*>(bm_s);
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        const int tile = tbase + 2 * q;
-                        const uint32_t off = meta16[tile * 8 + r_in_tile];
-                        const uint32_t mask = valid ? bm_bytes[tile * 8 + r_in_tile] : 0u;
-                        uint32_t o4[4];
-                        expand_row(val_s + off, mask, o4);
-                        a[4 * q + 0] = o4[0];
-                        a[4 * q + 1] = o4[1];
-                        a[4 * q + 2] = o4[2];
-                        a[4 * q + 3] = o4[3];
-                    }
-                }
+                for (int q = 0; q < 8; ++q) decode_unit(lds32(maddr + 32 * q), vbase, lut, a + 4 * q);
                 // ---- hand the dense rows to the tensor core through TMEM
                 bool fr = true;
                 if (around > 0) fr = mbar_wait(bar_afree + 8 * abuf, (around - 1) & 1, abort_flag);
                 fr = __all_sync(0xffffffffu, fr);
                 if (fr) {
                     tc_fence_after();
-                    tc_st_32x32b_x32(tmem_a0 + 32 * abuf + ((uint32_t)(quad * 32) << 16), a);
+                    const uint32_t ta = tmem_a0 + 32 * abuf + ((uint32_t)(quad * 32) << 16);
+                    tc_st_32x32b_x16(ta, a);
+                    tc_st_32x32b_x16(ta + 16, a + 16);
                     tc_wait_st();
                     tc_fence_before();
                 }
