@@ -26,6 +26,7 @@
 #include "common.cuh"
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <cstdio>
 #include <mutex>
 
 namespace spb {
@@ -42,16 +43,29 @@ constexpr int kDecodeWarp0 = 6;       // warps 6..
 constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kDecodeGroups);
 constexpr int kABufs = 2 * kDecodeGroups;  // A-operand buffers in TMEM (32 columns each)
 constexpr int kMaxStages = 24;
-// Per-row metadata of one stage: word = value offset (16 bit) | row mask << 16 | row count << 24.
-// Rows 0-3 and rows 4-7 of a tile live in two regions whose distance is 16 mod 32 words and every
-// 16-tile median group is shifted by 8 words, so that the 32 rows a warp reads at once fall into
-// 32 different banks.
-constexpr int kMetaRegionWords = 592;
-constexpr int kMetaBufBytes = 2 * kMetaRegionWords * 4;
-constexpr int kMetaBytes = ((kDecodeGroups * 2 * kMetaBufBytes + 1023) / 1024) * 1024;
+// Per-row metadata of one stage, 8 bytes per (tile, row):
+//   word 0  shared-memory byte address of the row's first packed value
+//   word 1  byte 0: 8 * low nibble of the row mask, byte 1: 8 * high nibble (offsets into the
+//           selector tables), byte 2: 2 * number of values in the row
+// Rows (2p, 2p+1) of all 128 tiles form piece p (16 bytes per tile); the pieces are 2080 bytes
+// apart, which makes both the 16-byte writes of pass 1 and the 8-byte reads of pass 2 free of
+// bank conflicts.
+constexpr int kMetaPieceBytes = 128 * 16 + 32;
+constexpr int kMetaBufBytes = 4 * kMetaPieceBytes;
+constexpr int kMetaBytes = ((kDecodeGroups * kMetaBufBytes + kDecodeGroups * 4 * 32 + 1023) / 1024) * 1024;
 constexpr int kHeaderBytes = 1024;
-constexpr int kLutOffset = 640;       // two 16-entry selector tables inside the header
 constexpr uint32_t kSpinLimit = 1u << 22;
+
+// Optional cycle accounting of the decode warps (debug builds only: -DSPB_TIMING).
+#ifdef SPB_TIMING
+#define SPB_TDECL long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t6 = 0
+#define SPB_T(x) x = clock64()
+#define SPB_ACC(i, v) tacc[i] += (v)
+#else
+#define SPB_TDECL
+#define SPB_T(x)
+#define SPB_ACC(i, v)
+#endif
 
 struct KernelParams {
     const uint16_t* vals;
@@ -172,6 +186,13 @@ __device__ __forceinline__ void tc_wait_ld()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 // AND-reduction of a predicate over the `n` threads of named barrier `id`.
 __device__ __forceinline__ bool bar_and(int id, int n, bool pred)
 {
@@ -245,62 +266,72 @@ __device__ __forceinline__ void lds32x3(uint32_t addr, uint32_t& a, uint32_t& b,
                  : "r"(addr));
 }
 
-// Selector tables for expanding a row segment with byte permutes.  A row's 8-bit mask is split in
-// two nibbles.  The low nibble's (up to 4) values are the first values of the row, the high
-// nibble's the last, so the low half is expanded from a window starting at the row's first value
-// and the high half from a window ending at its last value.
-//   low  entry: sel(pos 0,1 from {v0,v1 | zero})  |  sel(pos 2,3 from {v0..v3}) << 16
-//   high entry: sel(pos 4,5 from {v[k-4..k-1]})   |  sel(pos 6,7 from {v[k-2],v[k-1] | zero}) << 16
-__device__ __forceinline__ uint32_t lut_low_entry(uint32_t n)
+__device__ __forceinline__ void lds64(uint32_t addr, uint32_t& a, uint32_t& b)
 {
-    const uint32_t b0 = n & 1, b1 = (n >> 1) & 1, b2 = (n >> 2) & 1;
-    const uint32_t p0 = b0 ? 0x10u : 0x54u;
-    const uint32_t p1 = b1 ? (b0 ? 0x32u : 0x10u) : 0x54u;
-    const uint32_t i2 = b0 + b1, i3 = i2 + b2;
-    const uint32_t s1 = (0x10u + 0x22u * i2) | ((0x10u + 0x22u * i3) << 8);
-    return (p0 | (p1 << 8)) | (s1 << 16);
-}
-__device__ __forceinline__ uint32_t lut_high_entry(uint32_t n)
-{
-    const uint32_t b5 = (n >> 1) & 1, b6 = (n >> 2) & 1, b7 = (n >> 3) & 1;
-    const uint32_t h4 = 3 - (b5 + b6 + b7), h5 = 3 - (b6 + b7);
-    const uint32_t s2 = (0x10u + 0x22u * h4) | ((0x10u + 0x22u * h5) << 8);
-    const uint32_t p6 = b6 ? (b7 ? 0x10u : 0x32u) : 0x54u;
-    const uint32_t p7 = b7 ? 0x32u : 0x54u;
-    return s2 | ((p6 | (p7 << 8)) << 16);
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr));
 }
 
-// Expand one 8-element row segment described by `meta` (see kMetaRegionWords) into 4 registers
-// of packed fp16.  vbase: shared address of the stage's value region; lut: shared address of the
-// selector tables.
-__device__ __forceinline__ void decode_unit(uint32_t meta, uint32_t vbase, uint32_t lut, uint32_t* o)
+// Selector tables for expanding a row segment with byte permutes.  A row's 8-bit mask is split in
+// two nibbles.  The low nibble's (up to 4) values are the first values of the row, the high
+// nibble's the last, so positions 0-3 are filled from a 4-value window starting at the row's first
+// value and positions 4-7 from a 4-value window ending at its last value.  Every output register
+// (two positions) is one permute of a 2-value window and a zero register:
+//   pair_sel(lo, hi, first): selector placing the window's values at the kept positions.
+// Low-nibble entry  {sel(pos 0,1) | window(pos 2,3) << 16, sel(pos 2,3)}
+// High-nibble entry {sel(pos 6,7) | window(pos 4,5) << 16, sel(pos 4,5)}
+// where window(...) is the permute selector that cuts the 2-value window out of the 4-value one.
+__device__ __forceinline__ uint32_t pair_sel_bottom(uint32_t lo, uint32_t hi)
 {
-    const uint32_t off2 = (meta << 1) & 0x1fffeu;  // byte offset of the row's first value
-    const uint32_t k2 = (meta >> 23) & 0x1eu;      // 2 * number of values in the row
-    const uint32_t mask = (meta >> 16) & 0xffu;
-    uint32_t x0, x1, x2, y0, y1, y2;
-    lds32x3(vbase + (off2 & ~3u), x0, x1, x2);
-    const uint32_t ot2 = off2 + k2 - 8u;           // byte offset of the value 4 before the row's end
-    lds32x3(vbase + (ot2 & ~3u), y0, y1, y2);
-    const uint32_t L = lds32(lut + ((mask & 15u) << 2));
-    const uint32_t H = lds32(lut + 64u + ((mask >> 4) << 2));
-    const uint32_t selb = 0x3210u + ((off2 >> 1) & 1u) * 0x2222u;
-    const uint32_t selt = 0x3210u + ((ot2 >> 1) & 1u) * 0x2222u;
-    const uint32_t b0 = prmt(x0, x1, selb), b1 = prmt(x1, x2, selb);
-    const uint32_t t0 = prmt(y0, y1, selt), t1 = prmt(y1, y2, selt);
-    // 0xffff per kept position: mask bit -> sign bit of a byte -> replicated by the permute
-    const uint32_t z1 = (mask & 0x0cu) * 0x1020u, z2 = (mask & 0x30u) * 0x0408u;
-    const uint32_t k1 = prmt(z1, z1, 0x9988u), k2m = prmt(z2, z2, 0x9988u);
-    o[0] = prmt(b0, 0u, L);
-    o[1] = prmt(b0, b1, L >> 16) & k1;
-    o[2] = prmt(t0, t1, H) & k2m;
-    o[3] = prmt(t1, 0u, H >> 16);
+    // window = {next value, the one after}; zero register in bytes 4..7
+    const uint32_t p_lo = lo ? 0x10u : 0x54u;
+    const uint32_t p_hi = hi ? (lo ? 0x32u : 0x10u) : 0x54u;
+    return p_lo | (p_hi << 8);
+}
+__device__ __forceinline__ uint32_t pair_sel_top(uint32_t lo, uint32_t hi)
+{
+    // window = {second to last value, last value}
+    const uint32_t p_hi = hi ? 0x32u : 0x54u;
+    const uint32_t p_lo = lo ? (hi ? 0x10u : 0x32u) : 0x54u;
+    return p_lo | (p_hi << 8);
+}
+__device__ __forceinline__ uint2 lut_low_entry(uint32_t n)
+{
+    const uint32_t b0 = n & 1, b1 = (n >> 1) & 1, b2 = (n >> 2) & 1, b3 = (n >> 3) & 1;
+    const uint32_t win = 0x3210u + 0x2222u * (b0 + b1);  // values b0+b1, b0+b1+1 of the 4-value window
+    return make_uint2(pair_sel_bottom(b0, b1) | (win << 16), pair_sel_bottom(b2, b3));
+}
+__device__ __forceinline__ uint2 lut_high_entry(uint32_t n)
+{
+    const uint32_t b4 = n & 1, b5 = (n >> 1) & 1, b6 = (n >> 2) & 1, b7 = (n >> 3) & 1;
+    const uint32_t win = 0x3210u + 0x2222u * (2 - (b6 + b7));  // the two values before those of pos 6,7
+    return make_uint2(pair_sel_top(b6, b7) | (win << 16), pair_sel_top(b4, b5));
+}
+
+// Expand one 8-element row segment described by its two metadata words into 4 registers of packed
+// fp16.  lut: shared address of the selector tables (a link-time constant).
+__device__ __forceinline__ void decode_unit(uint32_t w0, uint32_t w1, uint32_t lut, uint32_t* o)
+{
+    const uint32_t ilo = prmt(w1, 0u, 0x4440u), ihi = prmt(w1, 0u, 0x4441u), k2 = prmt(w1, 0u, 0x4442u);
+    uint32_t x0, x1, x2, y0, y1, y2, l0, l1, h0, h1;
+    lds32x3(w0 & ~3u, x0, x1, x2);
+    const uint32_t wt = w0 + k2 - 8u;  // address of the value 4 before the row's end
+    lds32x3(wt & ~3u, y0, y1, y2);
+    lds64(lut + ilo, l0, l1);
+    lds64(lut + 128u + ihi, h0, h1);
+    const uint32_t sb = w0 << 3, st = wt << 3;  // funnel shifts use the low 5 bits: 0 or 16
+    const uint32_t b0 = __funnelshift_r(x0, x1, sb), b1 = __funnelshift_r(x1, x2, sb);
+    const uint32_t t0 = __funnelshift_r(y0, y1, st), t1 = __funnelshift_r(y1, y2, st);
+    o[0] = prmt(b0, 0u, l0);
+    o[1] = prmt(prmt(b0, b1, l0 >> 16), 0u, l1);
+    o[2] = prmt(prmt(t0, t1, h0 >> 16), 0u, h1);
+    o[3] = prmt(t1, 0u, h0);
 }
 
 template <int NPAD>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtensorMap tmap_b)
 {
+    __shared__ __align__(16) uint2 lut_tab[32];  // selector tables: low nibble [0,16), high nibble [16,32)
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled activation tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -324,15 +355,22 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t bar_full = smem_u32(bars);                         // [kMaxStages]
     const uint32_t bar_empty = bar_full + 8 * kMaxStages;             // [kMaxStages]
     const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [kABufs]
-    const uint32_t bar_afree = bar_aready + 8 * kABufs;               // [kABufs]
-    const uint32_t bar_accfull = bar_afree + 8 * kABufs;              // [2]
+    const uint32_t bar_accfull = bar_aready + 8 * kABufs;             // [2]
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kABufs + 4));
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + kABufs + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     uint8_t* meta_base = smem + kHeaderBytes;
     uint8_t* stage_base = smem + kHeaderBytes + kMetaBytes;
 
-    constexpr uint32_t kTmemCols = (2 * NPAD + 32 * kABufs) <= 256 ? 256 : 512;
+    // Back-to-back tcgen05.mma into one accumulator are serialised by the tensor core, and at these
+    // tiny N every instruction is pure latency, so the four k-steps of a k-tile go to different
+    // accumulators (summed in the epilogue).  Wide activation tiles get fewer, single-buffered ones
+    // to stay inside the 512 TMEM columns.
+    constexpr int kNAcc = NPAD <= 64 ? 4 : 2;
+    constexpr int kAccBufs = NPAD <= 32 ? 2 : 1;
+    constexpr uint32_t kAccCols = kAccBufs * kNAcc * NPAD;
+    static_assert(kAccCols + 32 * kABufs <= 512, "TMEM budget");
+    constexpr uint32_t kTmemCols = (kAccCols + 32 * kABufs) <= 256 ? 256 : 512;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kMaxStages; ++i) {
@@ -341,7 +379,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
         for (int i = 0; i < kABufs; ++i) {
             mbar_init(bar_aready + 8 * i, 4);
-            mbar_init(bar_afree + 8 * i, 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_accfull + 8 * i, 1);
@@ -351,9 +388,8 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (threadIdx.x >= 32 && threadIdx.x < 64) {
-        uint32_t* lut = reinterpret_cast<uint32_t*>(smem + kLutOffset);
         const uint32_t n = threadIdx.x - 32;
-        lut[n] = n < 16 ? lut_low_entry(n) : lut_high_entry(n - 16);
+        lut_tab[n] = n < 16 ? lut_low_entry(n) : lut_high_entry(n - 16);
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
@@ -365,97 +401,131 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
-    const uint32_t tmem_a0 = tmem_base + 2 * NPAD;
+    const uint32_t tmem_a0 = tmem_base + kAccCols;
 
-    if (S < 2) {
+    if (S < 4) {
         // Not enough shared memory for a pipeline (cannot happen with the launch configuration
         // used by the host code); leave cleanly.
         if (threadIdx.x == 0) atomicOr(p.status, (int)kStatusBadOffsets);
     } else if (warp == kProducerWarp) {
         // ================================================================= producer
-        uint32_t it = 0;
+        // Lane j of the warp issues every copy of one k-tile, so `batch` k-tiles are set up in
+        // parallel; batch <= S/2 keeps at least half of the ring in flight while a batch is refilled.
+        const int batch = S >= 16 ? 8 : (S >= 8 ? 4 : (S >= 4 ? 2 : 1));
+        uint32_t slot0 = 0, round0 = 0;  // ring position of the next k-tile
         bool ok = true;
         for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
             const Item w = decode_item(p, item);
             const bool chunk1 = (2 * w.y + 1) < p.gm_total;
             const size_t g_row0 = (size_t)(2 * w.y) * p.kt_total + w.k0;
-            for (int kk0 = 0; kk0 < w.nk && ok; kk0 += 32) {
+            for (int kk0 = 0; kk0 < w.nk && ok; kk0 += batch) {
                 const int kk = kk0 + lane;
-                int o0a = 0, o0b = 0, o1a = 0, o1b = 0;
-                if (kk < w.nk) {
-                    o0a = __ldg(p.gtile + g_row0 + kk);
-                    o0b = __ldg(p.gtile + g_row0 + kk + 1);
+                const int n_here = min(batch, w.nk - kk0);
+                bool mine_ok = true;
+                if (lane < n_here) {
+                    const size_t g0 = g_row0 + kk;
+                    const int a0 = __ldg(p.gtile + g0), b0 = __ldg(p.gtile + g0 + 1);
+                    int a1 = 0, b1 = 0;
                     if (chunk1) {
-                        o1a = __ldg(p.gtile + g_row0 + p.kt_total + kk);
-                        o1b = __ldg(p.gtile + g_row0 + p.kt_total + kk + 1);
+                        a1 = __ldg(p.gtile + g0 + p.kt_total);
+                        b1 = __ldg(p.gtile + g0 + p.kt_total + 1);
                     }
-                }
-                const int n_here = min(32, w.nk - kk0);
-                for (int j = 0; j < n_here && ok; ++j) {
-                    const int a0 = __shfl_sync(0xffffffffu, o0a, j), b0 = __shfl_sync(0xffffffffu, o0b, j);
-                    const int a1 = __shfl_sync(0xffffffffu, o1a, j), b1 = __shfl_sync(0xffffffffu, o1b, j);
-                    if (lane == 0) {
-                        const uint32_t slot = it % (uint32_t)S, round = it / (uint32_t)S;
-                        if (round > 0) ok = mbar_wait(bar_empty + 8 * slot, (round - 1) & 1, abort_flag);
-                        if (ok) {
-                            uint32_t n0 = (uint32_t)(b0 - a0) * 2, n1 = (uint32_t)(b1 - a1) * 2;
-                            if (b0 < a0 || n0 > vmax || b1 < a1 || n1 > vmax) {
-                                atomicOr(p.status, (int)kStatusBadOffsets);
-                                n0 = 0;
-                                n1 = 0;
-                            }
-                            const uint32_t full = bar_full + 8 * slot;
-                            const uint32_t sbase = smem_u32(stage_base + (size_t)slot * stage_bytes);
-                            const uint32_t tx = kBTile + n0 + n1 + (chunk1 ? 2u : 1u) * (512u + 16u);
-                            mbar_expect_tx(full, tx);
-                            const size_t g0 = g_row0 + kk0 + j;
-                            tma_load_2d(sbase, &tmap_b, (w.k0 + kk0 + j) * 64, w.nt * NPAD, full);
-                            if (n0) bulk_g2s(sbase + off_v0, p.vals + a0, n0, full);
-                            bulk_g2s(sbase + off_bm, p.bitmap + g0 * 64, 512, full);
-                            bulk_g2s(sbase + off_mt, p.mtile + g0 * 4, 16, full);
-                            if (chunk1) {
-                                const size_t g1 = g0 + p.kt_total;
-                                if (n1) bulk_g2s(sbase + off_v1, p.vals + a1, n1, full);
-                                bulk_g2s(sbase + off_bm + 512, p.bitmap + g1 * 64, 512, full);
-                                bulk_g2s(sbase + off_mt + 16, p.mtile + g1 * 4, 16, full);
-                            }
+                    uint32_t slot = slot0 + (uint32_t)lane, round = round0;
+                    if (slot >= (uint32_t)S) {
+                        slot -= (uint32_t)S;
+                        ++round;
+                    }
+                    if (round > 0) mine_ok = mbar_wait(bar_empty + 8 * slot, (round - 1) & 1, abort_flag);
+                    if (mine_ok) {
+                        uint32_t n0 = (uint32_t)(b0 - a0) * 2, n1 = (uint32_t)(b1 - a1) * 2;
+                        if (b0 < a0 || n0 > vmax || b1 < a1 || n1 > vmax) {
+                            atomicOr(p.status, (int)kStatusBadOffsets);
+                            n0 = 0;
+                            n1 = 0;
+                        }
+                        const uint32_t full = bar_full + 8 * slot;
+                        const uint32_t sbase = smem_u32(stage_base) + slot * stage_bytes;
+                        const uint32_t tx = kBTile + n0 + n1 + (chunk1 ? 2u : 1u) * (512u + 16u);
+                        mbar_expect_tx(full, tx);
+                        tma_load_2d(sbase, &tmap_b, (w.k0 + kk) * 64, w.nt * NPAD, full);
+                        if (n0) bulk_g2s(sbase + off_v0, p.vals + a0, n0, full);
+                        bulk_g2s(sbase + off_bm, p.bitmap + g0 * 64, 512, full);
+                        bulk_g2s(sbase + off_mt, p.mtile + g0 * 4, 16, full);
+                        if (chunk1) {
+                            const size_t g1 = g0 + p.kt_total;
+                            if (n1) bulk_g2s(sbase + off_v1, p.vals + a1, n1, full);
+                            bulk_g2s(sbase + off_bm + 512, p.bitmap + g1 * 64, 512, full);
+                            bulk_g2s(sbase + off_mt + 16, p.mtile + g1 * 4, 16, full);
                         }
                     }
-                    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-                    ++it;
+                }
+                ok = __all_sync(0xffffffffu, mine_ok);
+                slot0 += (uint32_t)n_here;
+                if (slot0 >= (uint32_t)S) {
+                    slot0 -= (uint32_t)S;
+                    ++round0;
                 }
             }
         }
     } else if (warp == kMmaWarp) {
         // ================================================================= MMA issuer
-        if (lane == 0) {
+        // The dense A rows of a k-tile are ready when its four decode warps have arrived on
+        // aready[abuf]; they only arrive after the stage's full barrier completed, so the
+        // activation tile has landed too.  One commit per k-tile arrives on the stage's empty
+        // barrier: it tells the producer that the activation tile may be overwritten and the
+        // decode warps that the TMEM A buffer may be rewritten.
+        // The whole warp runs the loop with warp-uniform state (so addresses and descriptors stay in
+        // uniform registers); one elected lane issues.
+        {
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            uint32_t it = 0, idx = 0;
+            uint32_t idx = 0, slot = 0, abuf = 0, around = 0;
+            const uint32_t stage0 = smem_u32(stage_base);
             bool ok = true;
+            SPB_TDECL;
             for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
                 const Item w = decode_item(p, item);
                 if (w.nk == 0) continue;
-                const uint32_t accbuf = idx & 1;
-                if (idx >= 2) ok = mbar_wait(bar_accempty + 8 * accbuf, ((idx >> 1) - 1) & 1, abort_flag);
-                const uint32_t d_tmem = tmem_base + accbuf * NPAD;
-                for (int kk = 0; kk < w.nk && ok; ++kk, ++it) {
-                    const uint32_t slot = it % (uint32_t)S, round = it / (uint32_t)S;
-                    const uint32_t abuf = it % kABufs, around = it / kABufs;
-                    ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag) &&
-                         mbar_wait(bar_aready + 8 * abuf, around & 1, abort_flag);
+                const uint32_t accbuf = idx % kAccBufs;
+                if (idx >= (uint32_t)kAccBufs)
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_accempty + 8 * accbuf, ((idx / kAccBufs) - 1) & 1, abort_flag));
+                const uint32_t d_tmem = tmem_base + accbuf * (kNAcc * NPAD);
+                for (int kk = 0; kk < w.nk && ok; ++kk) {
+                    SPB_T(t0);
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_aready + 8 * abuf, around & 1, abort_flag));
+                    SPB_T(t1);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t bdesc = make_b_desc(smem_u32(stage_base + (size_t)slot * stage_bytes));
+                    SPB_T(t3);
+                    const uint64_t bdesc = make_b_desc(stage0 + slot * stage_bytes);
                     const uint32_t a_tmem = tmem_a0 + 32 * abuf;
+                    if (elect_one()) {
 #pragma unroll
-                    for (int s = 0; s < 4; ++s)
-                        tc_mma_ts(d_tmem, a_tmem + 8 * s, bdesc + 2 * s, idesc, (kk > 0 || s > 0) ? 1u : 0u);
-                    tc_commit(bar_afree + 8 * abuf);
-                    tc_commit(bar_empty + 8 * slot);
+                        for (int s = 0; s < 4; ++s)
+                            tc_mma_ts(d_tmem + (s % kNAcc) * NPAD, a_tmem + 8 * s, bdesc + 2 * s, idesc,
+                                      (kk > 0 || s >= kNAcc) ? 1u : 0u);
+                        SPB_T(t4);
+                        tc_commit(bar_empty + 8 * slot);
+                    }
+                    __syncwarp();
+                    SPB_T(t5);
+                    SPB_ACC(2, t3 - t1); SPB_ACC(3, t4 - t3); SPB_ACC(4, t5 - t4);
+                    if (++slot == (uint32_t)S) slot = 0;
+                    if (++abuf == kABufs) {
+                        abuf = 0;
+                        ++around;
+                    }
+                    SPB_T(t2);
+                    SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
                 }
-                if (ok) tc_commit(bar_accfull + 8 * accbuf);
+                if (ok && elect_one()) tc_commit(bar_accfull + 8 * accbuf);
+                __syncwarp();
                 ++idx;
             }
+#ifdef SPB_TIMING
+            if (blockIdx.x == 0 && lane == 0)
+                printf("mma: n=%lld wait_aready=%lld issue=%lld (fence=%lld mma4=%lld commit=%lld)\n", tacc[6],
+                       tacc[0] / tacc[6], tacc[1] / tacc[6], tacc[2] / tacc[6], tacc[3] / tacc[6], tacc[4] / tacc[6]);
+#endif
         }
         __syncwarp();
     } else if (warp < kDecodeWarp0) {
@@ -475,16 +545,24 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 }
                 continue;
             }
-            const uint32_t accbuf = idx & 1;
-            ok = mbar_wait(bar_accfull + 8 * accbuf, (idx >> 1) & 1, abort_flag);
+            const uint32_t accbuf = idx % kAccBufs;
+            ok = mbar_wait(bar_accfull + 8 * accbuf, (idx / kAccBufs) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + accbuf * NPAD;
+            const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + accbuf * (kNAcc * NPAD);
 #pragma unroll
             for (int c = 0; c < NPAD / 16; ++c) {
                 uint32_t r[16];
                 tc_ld_32x32b_x16(t_acc + 16 * c, r);
+#pragma unroll
+                for (int j = 1; j < kNAcc; ++j) {
+                    uint32_t r2[16];
+                    tc_ld_32x32b_x16(t_acc + j * NPAD + 16 * c, r2);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) r[n] = __float_as_uint(__uint_as_float(r[n]) + __uint_as_float(r2[n]));
+                }
                 tc_wait_ld();
                 if (c == NPAD / 16 - 1) {
                     tc_fence_before();
@@ -502,92 +580,130 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
     } else {
         // ================================================================= decode
+        // Every decode warp works alone: the 32 weight rows of its TMEM lane quadrant cross exactly
+        // the 32 bitmap tiles 32*quad .. 32*quad+31 of the stage, so the tile metadata a warp
+        // needs in pass 2 is the metadata its own lanes produce in pass 1.
         const int dw = warp - kDecodeWarp0;
         const int group = dw >> 2;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;      // weight row inside the 128-row block == tile index in pass 1
-        const int bar_id = 1 + group;
-        uint8_t* meta_g = meta_base + group * (2 * kMetaBufBytes);
-        const uint32_t lut = smem_u32(smem + kLutOffset);
+        const uint32_t meta = smem_u32(meta_base + group * kMetaBufBytes);
+        uint8_t* cnt_s = meta_base + kDecodeGroups * kMetaBufBytes + dw * 32;  // 32 tile counts of this warp
+        const uint32_t lut = smem_u32(lut_tab);
         // pass 1: this thread owns tile `row` of the stage (tile t of chunk t>>6)
         const int chunk = row >> 6, rr = row & 63;
-        const uint32_t p1_word = (uint32_t)row * 4 + 8 * (uint32_t)(row >> 4);
+        const uint32_t p1_addr = meta + (uint32_t)row * 16;
+        // byte masks selecting, in the 16 counts of this lane's median tile, the tiles before its own
+        uint32_t before[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int n = (lane & 15) - 4 * i;
+            before[i] = n >= 4 ? 0xffffffffu : (n > 0 ? (1u << (8 * n)) - 1u : 0u);
+        }
         // pass 2: the 8 tiles crossing this weight row are tbase + 2q, q = 0..7
         const int tbase = chunk * 64 + 16 * (rr >> 4) + ((rr >> 3) & 1);
         const int r_in_tile = rr & 7;
-        const uint32_t p2_word = (uint32_t)(r_in_tile >> 2) * kMetaRegionWords + (uint32_t)tbase * 4 +
-                                 (uint32_t)(r_in_tile & 3) + 8 * (uint32_t)(tbase >> 4);
+        const uint32_t maddr = meta + (uint32_t)(r_in_tile >> 1) * kMetaPieceBytes + (uint32_t)tbase * 16 +
+                               (uint32_t)(r_in_tile & 1) * 8;
+        const uint32_t stage0 = smem_u32(stage_base);
 
-        uint32_t it = 0, mine = 0;
+        // ring position of the next k-tile this group decodes; it advances by kDecodeGroups
+        uint32_t slot = (uint32_t)group, round = 0;
+        uint32_t abuf = (uint32_t)group, mine = 0;
+        uint32_t bar_old = 0, par_old = 0, bar_new = 0, par_new = 0;  // empty barriers of this group's last two k-tiles
+        int skip = group;  // k-tiles of the stream to pass over before the next one of this group
         bool ok = true;
+        SPB_TDECL;
         for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
             const Item w = decode_item(p, item);
             const bool chunk1 = (2 * w.y + 1) < p.gm_total;
             const bool valid = (chunk == 0) || chunk1;
-            for (int kk = 0; kk < w.nk; ++kk, ++it) {
-                if ((int)(it % kDecodeGroups) != group) continue;
-                const uint32_t slot = it % (uint32_t)S, round = it / (uint32_t)S;
-                const uint32_t abuf = it % kABufs, around = it / kABufs;
-                const bool got = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
-                const uint8_t* st = stage_base + (size_t)slot * stage_bytes;
-                uint32_t* meta = reinterpret_cast<uint32_t*>(meta_g + (mine & 1) * kMetaBufBytes);
-                ++mine;
+            for (int kk = skip; kk < w.nk; kk += kDecodeGroups) {
+                SPB_T(t0);
+                ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                SPB_T(t1);
+                const uint32_t st = stage0 + slot * stage_bytes;
                 // ---- pass 1: per-row value offsets, masks and counts of tile `row`
                 {
-                    uint2 bm = make_uint2(0u, 0u);
-                    int mt = 0;
-                    if (got && valid) {
-                        bm = reinterpret_cast<const uint2*>(st + off_bm)[row];
-                        mt = reinterpret_cast<const int*>(st + off_mt)[chunk * 4 + (rr >> 4)];
+                    uint32_t bmx = 0, bmy = 0, mt = 0;
+                    if (valid) {
+                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(bmx), "=r"(bmy) : "r"(st + off_bm + 8 * row));
+                        mt = lds32(st + off_mt + 4 * (chunk * 4 + (rr >> 4)));
                     }
                     // per-byte population counts (one byte of the bitmap = one tile row)
-                    uint32_t a = bm.x - ((bm.x >> 1) & 0x55555555u);
+                    uint32_t a = bmx - ((bmx >> 1) & 0x55555555u);
                     a = (a & 0x33333333u) + ((a >> 2) & 0x33333333u);
                     a = (a + (a >> 4)) & 0x0f0f0f0fu;
-                    uint32_t b = bm.y - ((bm.y >> 1) & 0x55555555u);
+                    uint32_t b = bmy - ((bmy >> 1) & 0x55555555u);
                     b = (b & 0x33333333u) + ((b >> 2) & 0x33333333u);
                     b = (b + (b >> 4)) & 0x0f0f0f0fu;
                     const uint32_t ia = a * 0x01010101u, ib = b * 0x01010101u;  // inclusive byte prefixes
                     const uint32_t tl = ia >> 24;
-                    const int cnt = (int)(tl + (ib >> 24));
-                    int x = cnt;                                               // 16-lane scan: tiles of a median tile
-#pragma unroll
-                    for (int d = 1; d < 16; d <<= 1) {
-                        const int y = __shfl_up_sync(0xffffffffu, x, d, 16);
-                        if ((lane & 15) >= d) x += y;
-                    }
-                    const uint32_t base = (uint32_t)chunk * (vmax >> 1) + (uint32_t)mt + (uint32_t)(x - cnt);
-                    const uint32_t base_hi = base + tl;
-                    const uint32_t ea = ia << 8, eb = ib << 8;                   // exclusive prefixes, byte 0 == 0
-                    uint4 lo4, hi4;
-                    uint32_t* lo_w = reinterpret_cast<uint32_t*>(&lo4);
-                    uint32_t* hi_w = reinterpret_cast<uint32_t*>(&hi4);
+                    cnt_s[lane] = (uint8_t)(tl + (ib >> 24));
+                    __syncwarp();
+                    // values of the tiles that precede this one inside its 16-tile median tile
+                    uint32_t c0, c1, c2, c3;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+                                 : "r"(smem_u32(cnt_s) + (lane & 16)));
+                    c0 &= before[0];
+                    c1 &= before[1];
+                    c2 &= before[2];
+                    c3 &= before[3];
+                    uint32_t h = (c0 & 0x00ff00ffu) + ((c0 >> 8) & 0x00ff00ffu) + (c1 & 0x00ff00ffu) +
+                                 ((c1 >> 8) & 0x00ff00ffu) + (c2 & 0x00ff00ffu) + ((c2 >> 8) & 0x00ff00ffu) +
+                                 (c3 & 0x00ff00ffu) + ((c3 >> 8) & 0x00ff00ffu);
+                    const uint32_t excl = (h & 0xffffu) + (h >> 16);
+                    // in halves from the stage's value region (vmax halves long); clamped so that corrupt
+                    // offsets can never point outside the stage (the bitmaps follow the values)
+                    const uint32_t base = min((uint32_t)chunk * (vmax >> 1) + mt + excl, vmax);
+                    const uint32_t abs_lo = st + off_v0 + 2 * base;  // address of the tile's first value
+                    const uint32_t abs_hi = abs_lo + 2 * tl;
+                    const uint32_t ea = ia << 8, eb = ib << 8;         // exclusive row prefixes, byte 0 == 0
+                    const uint32_t il_lo = (bmx & 0x0f0f0f0fu) << 3, ih_lo = (bmx >> 1) & 0x78787878u, k_lo = a << 1;
+                    const uint32_t il_hi = (bmy & 0x0f0f0f0fu) << 3, ih_hi = (bmy >> 1) & 0x78787878u, k_hi = b << 1;
+                    uint32_t w0[8], w1[8];
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
                         const uint32_t s1 = (uint32_t)r | ((uint32_t)(4 + r) << 4);
-                        const uint32_t s2 = (uint32_t)r | (4u << 8) | (5u << 12);
-                        lo_w[r] = prmt(ea, prmt(bm.x, a, s1), s2) + base;
-                        hi_w[r] = prmt(eb, prmt(bm.y, b, s1), s2) + base_hi;
+                        const uint32_t s2 = 0x0010u | ((uint32_t)(4 + r) << 8) | ((uint32_t)(4 + r) << 12);
+                        w0[r] = prmt(ea, 0u, 0x4440u | (uint32_t)r) * 2u + abs_lo;
+                        w0[4 + r] = prmt(eb, 0u, 0x4440u | (uint32_t)r) * 2u + abs_hi;
+                        w1[r] = prmt(prmt(il_lo, ih_lo, s1), k_lo, s2);
+                        w1[4 + r] = prmt(prmt(il_hi, ih_hi, s1), k_hi, s2);
                     }
-                    *reinterpret_cast<uint4*>(meta + p1_word) = lo4;
-                    *reinterpret_cast<uint4*>(meta + kMetaRegionWords + p1_word) = hi4;
+#pragma unroll
+                    for (int pc = 0; pc < 4; ++pc)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p1_addr + pc * kMetaPieceBytes),
+                                     "r"(w0[2 * pc]), "r"(w1[2 * pc]), "r"(w0[2 * pc + 1]), "r"(w1[2 * pc + 1])
+                                     : "memory");
                 }
-                ok = bar_and(bar_id, 128, got && !*abort_flag);
-                if (!ok) break;
+                SPB_T(t2);
+                __syncwarp();
+                SPB_T(t3);
                 // ---- pass 2: thread <-> weight row; gather its 64 values, 8 per tile
-                const uint32_t vbase = smem_u32(st + off_v0);
-                const uint32_t maddr = smem_u32(meta + p2_word);
+                uint32_t m0[8], m1[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) lds64(maddr + 32 * q, m0[q], m1[q]);
                 uint32_t a[32];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) decode_unit(lds32(maddr + 32 * q), vbase, lut, a + 4 * q);
-                // ---- hand the dense rows to the tensor core through TMEM
+                for (int q = 0; q < 4; ++q) decode_unit(m0[q], m1[q], lut, a + 4 * q);
+                // the TMEM A buffer was last read by the MMA of this group's k-tile before last
+                SPB_T(t4);
                 bool fr = true;
-                if (around > 0) fr = mbar_wait(bar_afree + 8 * abuf, (around - 1) & 1, abort_flag);
+                if (mine >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
                 fr = __all_sync(0xffffffffu, fr);
+                SPB_T(t5);
+                const uint32_t ta = tmem_a0 + 32 * abuf + ((uint32_t)(quad * 32) << 16);
                 if (fr) {
                     tc_fence_after();
-                    const uint32_t ta = tmem_a0 + 32 * abuf + ((uint32_t)(quad * 32) << 16);
                     tc_st_32x32b_x16(ta, a);
+                }
+#pragma unroll
+                for (int q = 4; q < 8; ++q) decode_unit(m0[q], m1[q], lut, a + 4 * q);
+                if (fr) {
                     tc_st_32x32b_x16(ta + 16, a + 16);
                     tc_wait_st();
                     tc_fence_before();
@@ -597,8 +713,36 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     if (fr) mbar_arrive(bar_aready + 8 * abuf);
                     mbar_arrive(bar_empty + 8 * slot);
                 }
+                ok = fr;
+                bar_old = bar_new;
+                par_old = par_new;
+                bar_new = bar_empty + 8 * slot;
+                par_new = round & 1;
+                ++mine;
+                slot += kDecodeGroups;
+                if (slot >= (uint32_t)S) {
+                    slot -= (uint32_t)S;
+                    ++round;
+                }
+                abuf += kDecodeGroups;
+                if (abuf >= kABufs) abuf -= kABufs;
+                SPB_T(t6);
+                SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(2, t3 - t2); SPB_ACC(3, t4 - t3);
+                SPB_ACC(4, t5 - t4); SPB_ACC(5, t6 - t5); SPB_ACC(6, 1);
+                if (!ok) break;
+            }
+            // first k-tile of the next item that belongs to this group
+            if (ok) {
+                const int rem = (w.nk - skip) % kDecodeGroups;
+                skip = w.nk <= skip ? skip - w.nk : (rem == 0 ? 0 : kDecodeGroups - rem);
             }
         }
+#ifdef SPB_TIMING
+        if (blockIdx.x == 0 && lane == 0)
+            printf("decode warp %d: n=%lld wait_full=%lld pass1=%lld sync=%lld pass2a=%lld wait_afree=%lld rest=%lld (avg clk)\n",
+                   dw, tacc[6], tacc[0] / tacc[6], tacc[1] / tacc[6], tacc[2] / tacc[6], tacc[3] / tacc[6],
+                   tacc[4] / tacc[6], tacc[5] / tacc[6]);
+#endif
     }
 
     // ---- teardown ----------------------------------------------------------------------------
@@ -699,19 +843,20 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     p.row_blocks = (p.gm_total + 1) / 2;
     p.n_tiles = (a.N + NPAD - 1) / NPAD;
     p.num_items = p.n_tiles * p.row_blocks * a.split_k;
-    p.smem_bytes = (uint32_t)di.max_smem;
+    const int dyn_smem = di.max_smem - 1024;  // the kernel also has a small static table
+    p.smem_bytes = (uint32_t)dyn_smem;
 
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(spmm_bitmap_tcgen05_kernel<NPAD>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
     const int grid = p.num_items < di.sms ? p.num_items : di.sms;
-    spmm_bitmap_tcgen05_kernel<NPAD><<<grid, kThreads, di.max_smem, s>>>(p, tmap);
+    spmm_bitmap_tcgen05_kernel<NPAD><<<grid, kThreads, dyn_smem, s>>>(p, tmap);
     return cudaGetLastError();
 }
 
