@@ -403,7 +403,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t tmem_base = *tmem_holder;
     const uint32_t tmem_a0 = tmem_base + kAccCols;
 
-    if (S < 4) {
+    // Each decode group owns two TMEM A buffers when the ring is deeper than 2 * groups (the reuse
+    // wait then looks two of the group's k-tiles back), otherwise one.
+    const bool two_deep = S > 2 * kDecodeGroups;
+    const uint32_t n_abufs = two_deep ? 2u * kDecodeGroups : (uint32_t)kDecodeGroups;
+    if (S <= kDecodeGroups) {
         // Not enough shared memory for a pipeline (cannot happen with the launch configuration
         // used by the host code); leave cleanly.
         if (threadIdx.x == 0) atomicOr(p.status, (int)kStatusBadOffsets);
@@ -510,7 +514,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     SPB_T(t5);
                     SPB_ACC(2, t3 - t1); SPB_ACC(3, t4 - t3); SPB_ACC(4, t5 - t4);
                     if (++slot == (uint32_t)S) slot = 0;
-                    if (++abuf == kABufs) {
+                    if (++abuf == n_abufs) {
                         abuf = 0;
                         ++around;
                     }
@@ -693,7 +697,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 // the TMEM A buffer was last read by the MMA of this group's k-tile before last
                 SPB_T(t4);
                 bool fr = true;
-                if (mine >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
+                if (two_deep) {
+                    if (mine >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
+                } else if (mine >= 1) {
+                    fr = mbar_wait(bar_new, par_new, abort_flag);
+                }
                 fr = __all_sync(0xffffffffu, fr);
                 SPB_T(t5);
                 const uint32_t ta = tmem_a0 + 32 * abuf + ((uint32_t)(quad * 32) << 16);
@@ -725,7 +733,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     ++round;
                 }
                 abuf += kDecodeGroups;
-                if (abuf >= kABufs) abuf -= kABufs;
+                if (abuf >= n_abufs) abuf -= n_abufs;
                 SPB_T(t6);
                 SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(2, t3 - t2); SPB_ACC(3, t4 - t3);
                 SPB_ACC(4, t5 - t4); SPB_ACC(5, t6 - t5); SPB_ACC(6, 1);

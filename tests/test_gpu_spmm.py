@@ -52,6 +52,8 @@ def _run(sp, A, B, split_k):
     (256, 2048, 1, 0.6, 1),
     (128, 4096, 16, 0.0, 1),     # fully dense tiles (4096 values per global tile)
     (128, 4096, 16, 1.0, 1),     # all-zero matrix
+    (256, 2048, 128, 0.0, 2),    # dense tiles with the widest activation tile: shallowest stage ring
+    (256, 1024, 64, 0.05, 1),
     (4096, 4096, 16, 0.5, 1),    # BASELINE config 1
     (4096, 4096, 16, 0.5, 6),
     (5120, 5120, 16, 0.6, 6),    # OPT-13B out-proj
