@@ -32,17 +32,23 @@
 namespace spb {
 namespace {
 
-#ifndef SPB_DECODE_GROUPS
-#define SPB_DECODE_GROUPS 3
-#endif
-constexpr int kDecodeGroups = SPB_DECODE_GROUPS;  // each group: 4 warps, one thread per weight row
+// Warp roles, by warpgroup (4 warps) so that each role can resize its register file share:
+//   warpgroup 0: warp 1 MMA issuer, warps 0, 2, 3 producers (each issues a share of the copies)
+//   warpgroup 1: epilogue (one warp per TMEM lane quadrant)
+//   warpgroup 2..: decode groups (one warp per quadrant each)
+constexpr int kKT = 4;                // k-tiles per pipeline stage == decode groups
+constexpr int kDecodeGroups = kKT;
 constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
-constexpr int kEpilogueWarp0 = 2;     // warps 2..5
-constexpr int kDecodeWarp0 = 6;       // warps 6..
+constexpr int kEpilogueWarp0 = 4;
+constexpr int kDecodeWarp0 = 8;
 constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kDecodeGroups);
-constexpr int kABufs = 2 * kDecodeGroups;  // A-operand buffers in TMEM (32 columns each)
-constexpr int kMaxStages = 24;
+// Registers per thread after the roles have resized (the launch gives every thread
+// 65536 / kThreads rounded down to a multiple of 8).
+constexpr int kRegsControl = 40, kRegsEpilogue = 56, kRegsDecode = 96;
+static_assert(128 * kRegsControl + 128 * kRegsEpilogue + 128 * kDecodeGroups * kRegsDecode <= 65536 - 2048,
+              "register budget (keep slack: a resize that can never be satisfied would block forever)");
+constexpr int kMaxStages = 8;
 // Per-row metadata of one stage, 8 bytes per (tile, row):
 //   word 0  shared-memory byte address of the row's first packed value
 //   word 1  byte 0: 8 * low nibble of the row mask, byte 1: 8 * high nibble (offsets into the
@@ -122,6 +128,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     return false;
 }
+// Same, for waits that last a whole work item: polls rarely so that the waiting warp leaves the
+// issue slots to the others.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        __nanosleep(400);
+    }
+    *abort_flag = 1;
+    return false;
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
 {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -185,6 +203,17 @@ __device__ __forceinline__ void tc_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[1
 __device__ __forceinline__ void tc_wait_ld()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Register-file resizing of the calling warpgroup (all of its warps must execute it).
+template <int N>
+__device__ __forceinline__ void reg_alloc()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 // True in exactly one lane of a converged warp.
 __device__ __forceinline__ bool elect_one()
@@ -340,13 +369,19 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // ---- carve-up ------------------------------------------------------------------------
+    // A stage holds kKT consecutive k-tiles of one 128-row block: the activation tiles, then for each
+    // of the two 64-row global-tile rows one contiguous run of packed values, the bitmaps and the
+    // median offsets, then the start of every global tile's values inside its run.
     int max_nnz = *p.max_nnz;
     if (max_nnz < 8) max_nnz = 8;
     if (max_nnz > 4096) max_nnz = 4096;
-    const uint32_t vmax = ((uint32_t)max_nnz * 2 + 127) & ~127u;  // bytes per value chunk
+    const uint32_t vmax = ((uint32_t)max_nnz * 2 + 127) & ~127u;  // bytes per global tile, upper bound
     constexpr uint32_t kBTile = NPAD * 128;
-    const uint32_t off_v0 = kBTile, off_v1 = kBTile + vmax, off_bm = kBTile + 2 * vmax, off_mt = off_bm + 1024;
-    const uint32_t stage_bytes = (off_mt + 32 + 1023) & ~1023u;
+    const uint32_t off_v0 = kKT * kBTile, off_v1 = off_v0 + kKT * vmax;
+    const uint32_t off_bm0 = off_v1 + kKT * vmax, off_bm1 = off_bm0 + kKT * 512;
+    const uint32_t off_mt0 = off_bm1 + kKT * 512, off_mt1 = off_mt0 + kKT * 16;
+    const uint32_t off_rel = off_mt1 + kKT * 16;  // [2][kKT] uint32: byte offset of a tile's values in its run
+    const uint32_t stage_bytes = (off_rel + 8 * kKT + 1023) & ~1023u;
     const uint32_t avail = p.smem_bytes - pad - kHeaderBytes - kMetaBytes;
     int S = (int)(avail / stage_bytes);
     if (S > kMaxStages) S = kMaxStages;
@@ -354,33 +389,31 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t bar_full = smem_u32(bars);                         // [kMaxStages]
     const uint32_t bar_empty = bar_full + 8 * kMaxStages;             // [kMaxStages]
-    const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [kABufs]
-    const uint32_t bar_accfull = bar_aready + 8 * kABufs;             // [2]
+    const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [2]
+    const uint32_t bar_accfull = bar_aready + 16;                     // [2]
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + kABufs + 4));
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 6));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     uint8_t* meta_base = smem + kHeaderBytes;
-    uint8_t* stage_base = smem + kHeaderBytes + kMetaBytes;
+    const uint32_t stage0 = smem_u32(smem + kHeaderBytes + kMetaBytes);
 
     // Back-to-back tcgen05.mma into one accumulator are serialised by the tensor core, and at these
     // tiny N every instruction is pure latency, so the four k-steps of a k-tile go to different
-    // accumulators (summed in the epilogue).  Wide activation tiles get fewer, single-buffered ones
-    // to stay inside the 512 TMEM columns.
-    constexpr int kNAcc = NPAD <= 64 ? 4 : 2;
+    // accumulators (summed in the epilogue).
+    constexpr int kNAcc = 4;
     constexpr int kAccBufs = NPAD <= 32 ? 2 : 1;
     constexpr uint32_t kAccCols = kAccBufs * kNAcc * NPAD;
-    static_assert(kAccCols + 32 * kABufs <= 512, "TMEM budget");
-    constexpr uint32_t kTmemCols = (kAccCols + 32 * kABufs) <= 256 ? 256 : 512;
+    constexpr uint32_t kACols = 2 * kKT * 32;  // two stages' worth of A operands
+    static_assert(kAccCols + kACols <= 512, "TMEM budget");
+    constexpr uint32_t kTmemCols = 512;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kMaxStages; ++i) {
             mbar_init(bar_full + 8 * i, 1);
-            mbar_init(bar_empty + 8 * i, 5);  // 4 decode warps + the MMA commit
-        }
-        for (int i = 0; i < kABufs; ++i) {
-            mbar_init(bar_aready + 8 * i, 4);
+            mbar_init(bar_empty + 8 * i, 4 * kKT + 1);  // every decode warp + the MMA commit
         }
         for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_aready + 8 * i, 4 * kKT);
             mbar_init(bar_accfull + 8 * i, 1);
             mbar_init(bar_accempty + 8 * i, 4);
         }
@@ -403,87 +436,132 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t tmem_base = *tmem_holder;
     const uint32_t tmem_a0 = tmem_base + kAccCols;
 
-    // Each decode group owns two TMEM A buffers when the ring is deeper than 2 * groups (the reuse
-    // wait then looks two of the group's k-tiles back), otherwise one.
-    const bool two_deep = S > 2 * kDecodeGroups;
-    const uint32_t n_abufs = two_deep ? 2u * kDecodeGroups : (uint32_t)kDecodeGroups;
-    if (S <= kDecodeGroups) {
-        // Not enough shared memory for a pipeline (cannot happen with the launch configuration
-        // used by the host code); leave cleanly.
+    // With three or more stages the A operands in TMEM are double-buffered per stage (a decode warp
+    // may overwrite a buffer once the MMAs of the stage two back have completed); otherwise single.
+    const bool two_deep = S >= 3;
+    if (S < 1) {
+        // A single stage does not fit (cannot happen with the launch configuration used by the host
+        // code); leave cleanly.
         if (threadIdx.x == 0) atomicOr(p.status, (int)kStatusBadOffsets);
-    } else if (warp == kProducerWarp) {
-        // ================================================================= producer
-        // Lane j of the warp issues every copy of one k-tile, so `batch` k-tiles are set up in
-        // parallel; batch <= S/2 keeps at least half of the ring in flight while a batch is refilled.
-        const int batch = S >= 16 ? 8 : (S >= 8 ? 4 : (S >= 4 ? 2 : 1));
-        uint32_t slot0 = 0, round0 = 0;  // ring position of the next k-tile
-        bool ok = true;
-        for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
-            const Item w = decode_item(p, item);
-            const bool chunk1 = (2 * w.y + 1) < p.gm_total;
-            const size_t g_row0 = (size_t)(2 * w.y) * p.kt_total + w.k0;
-            for (int kk0 = 0; kk0 < w.nk && ok; kk0 += batch) {
-                const int kk = kk0 + lane;
-                const int n_here = min(batch, w.nk - kk0);
-                bool mine_ok = true;
-                if (lane < n_here) {
-                    const size_t g0 = g_row0 + kk;
-                    const int a0 = __ldg(p.gtile + g0), b0 = __ldg(p.gtile + g0 + 1);
-                    int a1 = 0, b1 = 0;
-                    if (chunk1) {
-                        a1 = __ldg(p.gtile + g0 + p.kt_total);
-                        b1 = __ldg(p.gtile + g0 + p.kt_total + 1);
-                    }
-                    uint32_t slot = slot0 + (uint32_t)lane, round = round0;
-                    if (slot >= (uint32_t)S) {
-                        slot -= (uint32_t)S;
-                        ++round;
-                    }
-                    if (round > 0) mine_ok = mbar_wait(bar_empty + 8 * slot, (round - 1) & 1, abort_flag);
-                    if (mine_ok) {
-                        uint32_t n0 = (uint32_t)(b0 - a0) * 2, n1 = (uint32_t)(b1 - a1) * 2;
-                        if (b0 < a0 || n0 > vmax || b1 < a1 || n1 > vmax) {
-                            atomicOr(p.status, (int)kStatusBadOffsets);
-                            n0 = 0;
-                            n1 = 0;
-                        }
-                        const uint32_t full = bar_full + 8 * slot;
-                        const uint32_t sbase = smem_u32(stage_base) + slot * stage_bytes;
-                        const uint32_t tx = kBTile + n0 + n1 + (chunk1 ? 2u : 1u) * (512u + 16u);
+    } else if (warp < kEpilogueWarp0) {
+        reg_dealloc<kRegsControl>();
+        if (warp != kMmaWarp) {
+            // ================================================================= producers
+            // Issuing a bulk copy costs the issuing thread on the order of a hundred cycles, so the
+            // copies of a stage are shared by three warps that walk the same stage sequence:
+            //   warp 0  arms the full barrier, writes the run offsets, copies the packed values
+            //   warp 2  copies bitmaps and median offsets
+            //   warp 3  loads the activation tiles
+            const int prole = warp == 0 ? 0 : warp - 1;
+            // The global-tile offsets of a stage are fetched one stage ahead, so that their latency
+            // overlaps with the wait for a free stage and the issue of the previous copies.
+            auto fetch_offsets = [&](const Item& w, int kk0) -> int {
+                const int nv = min(kKT, w.nk - kk0);
+                const size_t g0 = (size_t)(2 * w.y) * p.kt_total + w.k0 + kk0;
+                const bool chunk1 = (2 * w.y + 1) < p.gm_total;
+                // lanes 0..nv: offsets of row 0's tiles; lanes 8..8+nv: row 1's
+                int v = 0;
+                if (lane <= nv) v = __ldg(p.gtile + g0 + lane);
+                if (chunk1 && lane >= 8 && lane - 8 <= nv) v = __ldg(p.gtile + g0 + p.kt_total + (lane - 8));
+                return v;
+            };
+            uint32_t slot = 0, round = 0;
+            bool ok = true;
+            SPB_TDECL;
+            int item = blockIdx.x, kk0 = 0;
+            Item w = decode_item(p, item < p.num_items ? item : 0);
+            while (item < p.num_items && w.nk == 0) {  // skip empty split-K ranges
+                item += gridDim.x;
+                if (item < p.num_items) w = decode_item(p, item);
+            }
+            int myoff = (prole == 0 && item < p.num_items) ? fetch_offsets(w, 0) : 0;
+            while (item < p.num_items && ok) {
+                const Item cw = w;
+                const int ckk0 = kk0;
+                const int cur_off = myoff;
+                // advance to the next stage and start fetching its offsets
+                kk0 += kKT;
+                if (kk0 >= w.nk) {
+                    kk0 = 0;
+                    do {
+                        item += gridDim.x;
+                        if (item < p.num_items) w = decode_item(p, item);
+                    } while (item < p.num_items && w.nk == 0);
+                }
+                if (prole == 0 && item < p.num_items) myoff = fetch_offsets(w, kk0);
+
+                const bool chunk1 = (2 * cw.y + 1) < p.gm_total;
+                const int nv = min(kKT, cw.nk - ckk0);
+                const size_t g0 = (size_t)(2 * cw.y) * p.kt_total + cw.k0 + ckk0;
+                const int a0 = __shfl_sync(0xffffffffu, cur_off, 0), e0 = __shfl_sync(0xffffffffu, cur_off, nv);
+                const int a1 = __shfl_sync(0xffffffffu, cur_off, 8), e1 = __shfl_sync(0xffffffffu, cur_off, 8 + nv);
+                SPB_T(t0);
+                if (round > 0) ok = mbar_wait(bar_empty + 8 * slot, (round - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                SPB_T(t1);
+                uint32_t n0 = (uint32_t)(e0 - a0) * 2, n1 = chunk1 ? (uint32_t)(e1 - a1) * 2 : 0u;
+                if (e0 < a0 || n0 > (uint32_t)nv * vmax || (chunk1 && (e1 < a1 || n1 > (uint32_t)nv * vmax))) {
+                    if (lane == 0) atomicOr(p.status, (int)kStatusBadOffsets);
+                    n0 = 0;
+                    n1 = 0;
+                }
+                const uint32_t sbase = stage0 + slot * stage_bytes;
+                const uint32_t full = bar_full + 8 * slot;
+                // where each global tile's values start inside the run (clamped: corrupt offsets must
+                // not lead the decode warps outside the stage)
+                if (prole == 0 && (lane < kKT || (lane >= 8 && lane < 8 + kKT))) {
+                    const uint32_t rel = (uint32_t)(cur_off - (lane < 8 ? a0 : a1)) * 2;
+                    const uint32_t idx = lane < 8 ? (uint32_t)lane : (uint32_t)(kKT + lane - 8);
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sbase + off_rel + 4 * idx),
+                                 "r"(min(rel, (uint32_t)kKT * vmax))
+                                 : "memory");
+                }
+                __syncwarp();
+                // one elected lane issues this warp's copies with warp-uniform operands
+                if (elect_one()) {
+                    if (prole == 0) {
+                        const uint32_t tx =
+                            (uint32_t)nv * kBTile + n0 + n1 + (chunk1 ? 2u : 1u) * (uint32_t)nv * (512u + 16u);
                         mbar_expect_tx(full, tx);
-                        tma_load_2d(sbase, &tmap_b, (w.k0 + kk) * 64, w.nt * NPAD, full);
                         if (n0) bulk_g2s(sbase + off_v0, p.vals + a0, n0, full);
-                        bulk_g2s(sbase + off_bm, p.bitmap + g0 * 64, 512, full);
-                        bulk_g2s(sbase + off_mt, p.mtile + g0 * 4, 16, full);
+                        if (n1) bulk_g2s(sbase + off_v1, p.vals + a1, n1, full);
+                    } else if (prole == 1) {
+                        bulk_g2s(sbase + off_bm0, p.bitmap + g0 * 64, (uint32_t)nv * 512u, full);
+                        bulk_g2s(sbase + off_mt0, p.mtile + g0 * 4, (uint32_t)nv * 16u, full);
                         if (chunk1) {
-                            const size_t g1 = g0 + p.kt_total;
-                            if (n1) bulk_g2s(sbase + off_v1, p.vals + a1, n1, full);
-                            bulk_g2s(sbase + off_bm + 512, p.bitmap + g1 * 64, 512, full);
-                            bulk_g2s(sbase + off_mt + 16, p.mtile + g1 * 4, 16, full);
+                            bulk_g2s(sbase + off_bm1, p.bitmap + (g0 + p.kt_total) * 64, (uint32_t)nv * 512u, full);
+                            bulk_g2s(sbase + off_mt1, p.mtile + (g0 + p.kt_total) * 4, (uint32_t)nv * 16u, full);
                         }
+                    } else {
+                        for (int j = 0; j < nv; ++j)  // activation tile of k-tile j
+                            tma_load_2d(sbase + (uint32_t)j * kBTile, &tmap_b, (cw.k0 + ckk0 + j) * 64, cw.nt * NPAD,
+                                        full);
                     }
                 }
-                ok = __all_sync(0xffffffffu, mine_ok);
-                slot0 += (uint32_t)n_here;
-                if (slot0 >= (uint32_t)S) {
-                    slot0 -= (uint32_t)S;
-                    ++round0;
+                __syncwarp();
+                SPB_T(t2);
+                SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
+                if (++slot == (uint32_t)S) {
+                    slot = 0;
+                    ++round;
                 }
             }
-        }
-    } else if (warp == kMmaWarp) {
-        // ================================================================= MMA issuer
-        // The dense A rows of a k-tile are ready when its four decode warps have arrived on
-        // aready[abuf]; they only arrive after the stage's full barrier completed, so the
-        // activation tile has landed too.  One commit per k-tile arrives on the stage's empty
-        // barrier: it tells the producer that the activation tile may be overwritten and the
-        // decode warps that the TMEM A buffer may be rewritten.
-        // The whole warp runs the loop with warp-uniform state (so addresses and descriptors stay in
-        // uniform registers); one elected lane issues.
-        {
+#ifdef SPB_TIMING
+            if (blockIdx.x == 0 && lane == 0)
+                printf("producer: stages=%lld wait_empty=%lld issue=%lld S=%d stage_bytes=%u\n", tacc[6], tacc[0] / tacc[6],
+                       tacc[1] / tacc[6], S, stage_bytes);
+#endif
+        } else if (warp == kMmaWarp) {
+            // ================================================================= MMA issuer
+            // The whole warp runs the loop with warp-uniform state (so addresses and descriptors stay
+            // in uniform registers); one elected lane issues.  A stage's A operands are ready when all
+            // decode warps have arrived on aready; they only arrive after the stage's full barrier
+            // completed, so the activation tiles have landed too.  One commit per stage arrives on
+            // its empty barrier: the producer may refill the stage and the decode warps may
+            // overwrite the TMEM A buffers.
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            uint32_t idx = 0, slot = 0, abuf = 0, around = 0;
-            const uint32_t stage0 = smem_u32(stage_base);
+            uint32_t idx = 0, slot = 0, sidx = 0;
             bool ok = true;
             SPB_TDECL;
             for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
@@ -491,35 +569,34 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 if (w.nk == 0) continue;
                 const uint32_t accbuf = idx % kAccBufs;
                 if (idx >= (uint32_t)kAccBufs)
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_accempty + 8 * accbuf, ((idx / kAccBufs) - 1) & 1, abort_flag));
+                    ok = __all_sync(0xffffffffu,
+                                    mbar_wait(bar_accempty + 8 * accbuf, ((idx / kAccBufs) - 1) & 1, abort_flag));
                 const uint32_t d_tmem = tmem_base + accbuf * (kNAcc * NPAD);
-                for (int kk = 0; kk < w.nk && ok; ++kk) {
+                for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT, ++sidx) {
+                    const int nv = min(kKT, w.nk - kk0);
+                    const uint32_t abuf = two_deep ? (sidx & 1u) : 0u;
+                    const uint32_t apar = two_deep ? ((sidx >> 1) & 1u) : (sidx & 1u);
                     SPB_T(t0);
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_aready + 8 * abuf, around & 1, abort_flag));
-                    SPB_T(t1);
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_aready + 8 * abuf, apar, abort_flag));
                     if (!ok) break;
+                    SPB_T(t1);
                     tc_fence_after();
-                    SPB_T(t3);
-                    const uint64_t bdesc = make_b_desc(stage0 + slot * stage_bytes);
-                    const uint32_t a_tmem = tmem_a0 + 32 * abuf;
+                    const uint32_t sbase = stage0 + slot * stage_bytes;
                     if (elect_one()) {
+                        for (int sub = 0; sub < nv; ++sub) {
+                            const uint64_t bdesc = make_b_desc(sbase + (uint32_t)sub * kBTile);
+                            const uint32_t a_tmem = tmem_a0 + (abuf * kKT + (uint32_t)sub) * 32;
 #pragma unroll
-                        for (int s = 0; s < 4; ++s)
-                            tc_mma_ts(d_tmem + (s % kNAcc) * NPAD, a_tmem + 8 * s, bdesc + 2 * s, idesc,
-                                      (kk > 0 || s >= kNAcc) ? 1u : 0u);
-                        SPB_T(t4);
+                            for (int s = 0; s < 4; ++s)
+                                tc_mma_ts(d_tmem + (s % kNAcc) * NPAD, a_tmem + 8 * s, bdesc + 2 * s, idesc,
+                                          (kk0 > 0 || sub > 0 || s >= kNAcc) ? 1u : 0u);
+                        }
                         tc_commit(bar_empty + 8 * slot);
                     }
                     __syncwarp();
-                    SPB_T(t5);
-                    SPB_ACC(2, t3 - t1); SPB_ACC(3, t4 - t3); SPB_ACC(4, t5 - t4);
-                    if (++slot == (uint32_t)S) slot = 0;
-                    if (++abuf == n_abufs) {
-                        abuf = 0;
-                        ++around;
-                    }
                     SPB_T(t2);
                     SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
+                    if (++slot == (uint32_t)S) slot = 0;
                 }
                 if (ok && elect_one()) tc_commit(bar_accfull + 8 * accbuf);
                 __syncwarp();
@@ -527,12 +604,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             }
 #ifdef SPB_TIMING
             if (blockIdx.x == 0 && lane == 0)
-                printf("mma: n=%lld wait_aready=%lld issue=%lld (fence=%lld mma4=%lld commit=%lld)\n", tacc[6],
-                       tacc[0] / tacc[6], tacc[1] / tacc[6], tacc[2] / tacc[6], tacc[3] / tacc[6], tacc[4] / tacc[6]);
+                printf("mma: stages=%lld wait_aready=%lld issue=%lld\n", tacc[6], tacc[0] / tacc[6], tacc[1] / tacc[6]);
 #endif
         }
-        __syncwarp();
     } else if (warp < kDecodeWarp0) {
+        reg_dealloc<kRegsEpilogue>();
         // ================================================================= epilogue
         const int quad = warp & 3;
         const int row_in_block = quad * 32 + lane;
@@ -550,7 +626,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 continue;
             }
             const uint32_t accbuf = idx % kAccBufs;
-            ok = mbar_wait(bar_accfull + 8 * accbuf, (idx / kAccBufs) & 1, abort_flag);
+            ok = mbar_wait_relaxed(bar_accfull + 8 * accbuf, (idx / kAccBufs) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -584,19 +660,25 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
     } else {
         // ================================================================= decode
-        // Every decode warp works alone: the 32 weight rows of its TMEM lane quadrant cross exactly
-        // the 32 bitmap tiles 32*quad .. 32*quad+31 of the stage, so the tile metadata a warp
-        // needs in pass 2 is the metadata its own lanes produce in pass 1.
+        // Decode group g (4 warps, one per TMEM lane quadrant) expands k-tile g of every stage.
+        // Every warp works alone: the 32 weight rows of its quadrant cross exactly the 32 bitmap
+        // tiles 32*quad .. 32*quad+31 of the k-tile, so the tile metadata a warp needs in pass 2 is
+        // the metadata its own lanes produce in pass 1.
+        reg_alloc<kRegsDecode>();
         const int dw = warp - kDecodeWarp0;
         const int group = dw >> 2;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;      // weight row inside the 128-row block == tile index in pass 1
         const uint32_t meta = smem_u32(meta_base + group * kMetaBufBytes);
-        uint8_t* cnt_s = meta_base + kDecodeGroups * kMetaBufBytes + dw * 32;  // 32 tile counts of this warp
+        uint8_t* cnt_s = meta_base + kKT * kMetaBufBytes + dw * 32;  // 32 tile counts of this warp
         const uint32_t lut = smem_u32(lut_tab);
-        // pass 1: this thread owns tile `row` of the stage (tile t of chunk t>>6)
+        // pass 1: this thread owns tile `row` of the k-tile (tile t of global-tile row t>>6)
         const int chunk = row >> 6, rr = row & 63;
         const uint32_t p1_addr = meta + (uint32_t)row * 16;
+        const uint32_t my_v = chunk ? off_v1 : off_v0;
+        const uint32_t my_bm = (chunk ? off_bm1 : off_bm0) + (uint32_t)group * 512 + 8 * (uint32_t)rr;
+        const uint32_t my_mt = (chunk ? off_mt1 : off_mt0) + (uint32_t)group * 16 + 4 * (uint32_t)(rr >> 4);
+        const uint32_t my_rel = off_rel + 4 * (uint32_t)(chunk * kKT + group);
         // byte masks selecting, in the 16 counts of this lane's median tile, the tiles before its own
         uint32_t before[4];
 #pragma unroll
@@ -609,147 +691,146 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         const int r_in_tile = rr & 7;
         const uint32_t maddr = meta + (uint32_t)(r_in_tile >> 1) * kMetaPieceBytes + (uint32_t)tbase * 16 +
                                (uint32_t)(r_in_tile & 1) * 8;
-        const uint32_t stage0 = smem_u32(stage_base);
 
-        // ring position of the next k-tile this group decodes; it advances by kDecodeGroups
-        uint32_t slot = (uint32_t)group, round = 0;
-        uint32_t abuf = (uint32_t)group, mine = 0;
-        uint32_t bar_old = 0, par_old = 0, bar_new = 0, par_new = 0;  // empty barriers of this group's last two k-tiles
-        int skip = group;  // k-tiles of the stream to pass over before the next one of this group
+        uint32_t slot = 0, round = 0, sidx = 0;
+        uint32_t bar_old = 0, par_old = 0, bar_new = 0, par_new = 0;  // empty barriers of the last two stages
         bool ok = true;
         SPB_TDECL;
         for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
             const Item w = decode_item(p, item);
             const bool chunk1 = (2 * w.y + 1) < p.gm_total;
             const bool valid = (chunk == 0) || chunk1;
-            for (int kk = skip; kk < w.nk; kk += kDecodeGroups) {
+            for (int kk0 = 0; kk0 < w.nk; kk0 += kKT, ++sidx) {
+                const bool active = group < w.nk - kk0;  // this group's k-tile exists in the stage
                 SPB_T(t0);
                 ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 SPB_T(t1);
                 const uint32_t st = stage0 + slot * stage_bytes;
-                // ---- pass 1: per-row value offsets, masks and counts of tile `row`
-                {
-                    uint32_t bmx = 0, bmy = 0, mt = 0;
-                    if (valid) {
-                        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(bmx), "=r"(bmy) : "r"(st + off_bm + 8 * row));
-                        mt = lds32(st + off_mt + 4 * (chunk * 4 + (rr >> 4)));
-                    }
-                    // per-byte population counts (one byte of the bitmap = one tile row)
-                    uint32_t a = bmx - ((bmx >> 1) & 0x55555555u);
-                    a = (a & 0x33333333u) + ((a >> 2) & 0x33333333u);
-                    a = (a + (a >> 4)) & 0x0f0f0f0fu;
-                    uint32_t b = bmy - ((bmy >> 1) & 0x55555555u);
-                    b = (b & 0x33333333u) + ((b >> 2) & 0x33333333u);
-                    b = (b + (b >> 4)) & 0x0f0f0f0fu;
-                    const uint32_t ia = a * 0x01010101u, ib = b * 0x01010101u;  // inclusive byte prefixes
-                    const uint32_t tl = ia >> 24;
-                    cnt_s[lane] = (uint8_t)(tl + (ib >> 24));
-                    __syncwarp();
-                    // values of the tiles that precede this one inside its 16-tile median tile
-                    uint32_t c0, c1, c2, c3;
-                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
-                                 : "r"(smem_u32(cnt_s) + (lane & 16)));
-                    c0 &= before[0];
-                    c1 &= before[1];
-                    c2 &= before[2];
-                    c3 &= before[3];
-                    uint32_t h = (c0 & 0x00ff00ffu) + ((c0 >> 8) & 0x00ff00ffu) + (c1 & 0x00ff00ffu) +
-                                 ((c1 >> 8) & 0x00ff00ffu) + (c2 & 0x00ff00ffu) + ((c2 >> 8) & 0x00ff00ffu) +
-                                 (c3 & 0x00ff00ffu) + ((c3 >> 8) & 0x00ff00ffu);
-                    const uint32_t excl = (h & 0xffffu) + (h >> 16);
-                    // in halves from the stage's value region (vmax halves long); clamped so that corrupt
-                    // offsets can never point outside the stage (the bitmaps follow the values)
-                    const uint32_t base = min((uint32_t)chunk * (vmax >> 1) + mt + excl, vmax);
-                    const uint32_t abs_lo = st + off_v0 + 2 * base;  // address of the tile's first value
-                    const uint32_t abs_hi = abs_lo + 2 * tl;
-                    const uint32_t ea = ia << 8, eb = ib << 8;         // exclusive row prefixes, byte 0 == 0
-                    const uint32_t il_lo = (bmx & 0x0f0f0f0fu) << 3, ih_lo = (bmx >> 1) & 0x78787878u, k_lo = a << 1;
-                    const uint32_t il_hi = (bmy & 0x0f0f0f0fu) << 3, ih_hi = (bmy >> 1) & 0x78787878u, k_hi = b << 1;
-                    uint32_t w0[8], w1[8];
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const uint32_t s1 = (uint32_t)r | ((uint32_t)(4 + r) << 4);
-                        const uint32_t s2 = 0x0010u | ((uint32_t)(4 + r) << 8) | ((uint32_t)(4 + r) << 12);
-                        w0[r] = prmt(ea, 0u, 0x4440u | (uint32_t)r) * 2u + abs_lo;
-                        w0[4 + r] = prmt(eb, 0u, 0x4440u | (uint32_t)r) * 2u + abs_hi;
-                        w1[r] = prmt(prmt(il_lo, ih_lo, s1), k_lo, s2);
-                        w1[4 + r] = prmt(prmt(il_hi, ih_hi, s1), k_hi, s2);
-                    }
-#pragma unroll
-                    for (int pc = 0; pc < 4; ++pc)
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p1_addr + pc * kMetaPieceBytes),
-                                     "r"(w0[2 * pc]), "r"(w1[2 * pc]), "r"(w0[2 * pc + 1]), "r"(w1[2 * pc + 1])
-                                     : "memory");
-                }
-                SPB_T(t2);
-                __syncwarp();
-                SPB_T(t3);
-                // ---- pass 2: thread <-> weight row; gather its 64 values, 8 per tile
-                uint32_t m0[8], m1[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q) lds64(maddr + 32 * q, m0[q], m1[q]);
                 uint32_t a[32];
+                if (active) {
+#if defined(SPB_EXP_NO_DECODE)
 #pragma unroll
-                for (int q = 0; q < 4; ++q) decode_unit(m0[q], m1[q], lut, a + 4 * q);
-                // the TMEM A buffer was last read by the MMA of this group's k-tile before last
-                SPB_T(t4);
-                bool fr = true;
-                if (two_deep) {
-                    if (mine >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
-                } else if (mine >= 1) {
-                    fr = mbar_wait(bar_new, par_new, abort_flag);
-                }
-                fr = __all_sync(0xffffffffu, fr);
-                SPB_T(t5);
-                const uint32_t ta = tmem_a0 + 32 * abuf + ((uint32_t)(quad * 32) << 16);
-                if (fr) {
-                    tc_fence_after();
-                    tc_st_32x32b_x16(ta, a);
-                }
+                    for (int q = 0; q < 32; ++q) a[q] = 0;
+                    uint32_t m0[8], m1[8];
+#else
+                    // ---- pass 1: per-row value addresses, table offsets and counts of tile `row`
+                    {
+                        uint32_t bmx = 0, bmy = 0, mt = 0, rel = 0;
+                        if (valid) {
+                            lds64(st + my_bm, bmx, bmy);
+                            mt = lds32(st + my_mt);
+                            rel = lds32(st + my_rel);
+                        }
+                        // per-byte population counts (one byte of the bitmap = one tile row)
+                        uint32_t ca = bmx - ((bmx >> 1) & 0x55555555u);
+                        ca = (ca & 0x33333333u) + ((ca >> 2) & 0x33333333u);
+                        ca = (ca + (ca >> 4)) & 0x0f0f0f0fu;
+                        uint32_t cb = bmy - ((bmy >> 1) & 0x55555555u);
+                        cb = (cb & 0x33333333u) + ((cb >> 2) & 0x33333333u);
+                        cb = (cb + (cb >> 4)) & 0x0f0f0f0fu;
+                        const uint32_t ia = ca * 0x01010101u, ib = cb * 0x01010101u;  // inclusive byte prefixes
+                        const uint32_t tl = ia >> 24;
+                        cnt_s[lane] = (uint8_t)(tl + (ib >> 24));
+                        __syncwarp();
+                        // values of the tiles that precede this one inside its 16-tile median tile
+                        uint32_t c0, c1, c2, c3;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+                                     : "r"(smem_u32(cnt_s) + (lane & 16)));
+                        c0 &= before[0];
+                        c1 &= before[1];
+                        c2 &= before[2];
+                        c3 &= before[3];
+                        const uint32_t h = (c0 & 0x00ff00ffu) + ((c0 >> 8) & 0x00ff00ffu) + (c1 & 0x00ff00ffu) +
+                                           ((c1 >> 8) & 0x00ff00ffu) + (c2 & 0x00ff00ffu) + ((c2 >> 8) & 0x00ff00ffu) +
+                                           (c3 & 0x00ff00ffu) + ((c3 >> 8) & 0x00ff00ffu);
+                        const uint32_t excl = (h & 0xffffu) + (h >> 16);
+                        // byte offset of the tile's first value in its run; clamped so that corrupt
+                        // median offsets can never point outside the stage (the bitmaps follow the values)
+                        const uint32_t in_run = min(rel + 2 * (mt + excl), (uint32_t)kKT * vmax);
+                        const uint32_t abs_lo = st + my_v + in_run;  // address of the tile's first value
+                        const uint32_t abs_hi = abs_lo + 2 * tl;
+                        const uint32_t ea = ia << 8, eb = ib << 8;    // exclusive row prefixes, byte 0 == 0
+                        const uint32_t il_lo = (bmx & 0x0f0f0f0fu) << 3, ih_lo = (bmx >> 1) & 0x78787878u, k_lo = ca << 1;
+                        const uint32_t il_hi = (bmy & 0x0f0f0f0fu) << 3, ih_hi = (bmy >> 1) & 0x78787878u, k_hi = cb << 1;
+                        uint32_t w0[8], w1[8];
 #pragma unroll
-                for (int q = 4; q < 8; ++q) decode_unit(m0[q], m1[q], lut, a + 4 * q);
-                if (fr) {
-                    tc_st_32x32b_x16(ta + 16, a + 16);
-                    tc_wait_st();
-                    tc_fence_before();
+                        for (int r = 0; r < 4; ++r) {
+                            const uint32_t s1 = (uint32_t)r | ((uint32_t)(4 + r) << 4);
+                            const uint32_t s2 = 0x0010u | ((uint32_t)(4 + r) << 8) | ((uint32_t)(4 + r) << 12);
+                            w0[r] = prmt(ea, 0u, 0x4440u | (uint32_t)r) * 2u + abs_lo;
+                            w0[4 + r] = prmt(eb, 0u, 0x4440u | (uint32_t)r) * 2u + abs_hi;
+                            w1[r] = prmt(prmt(il_lo, ih_lo, s1), k_lo, s2);
+                            w1[4 + r] = prmt(prmt(il_hi, ih_hi, s1), k_hi, s2);
+                        }
+#pragma unroll
+                        for (int pc = 0; pc < 4; ++pc)
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p1_addr + pc * kMetaPieceBytes),
+                                         "r"(w0[2 * pc]), "r"(w1[2 * pc]), "r"(w0[2 * pc + 1]), "r"(w1[2 * pc + 1])
+                                         : "memory");
+                    }
+                    __syncwarp();
+                    // ---- pass 2, first half: thread <-> weight row; gather its values, 8 per tile
+                    uint32_t m0[8], m1[8];
+#if defined(SPB_EXP_NO_PASS2)
+#pragma unroll
+                    for (int q = 0; q < 32; ++q) a[q] = 0;
+#else
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) lds64(maddr + 32 * q, m0[q], m1[q]);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) decode_unit(m0[q], m1[q], lut, a + 4 * q);
+#endif
+#endif
+                    // the TMEM A buffer may be rewritten once the MMAs that read it have completed
+                    bool fr = true;
+                    if (two_deep) {
+                        if (sidx >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
+                    } else if (sidx >= 1) {
+                        fr = mbar_wait(bar_new, par_new, abort_flag);
+                    }
+                    fr = __all_sync(0xffffffffu, fr);
+                    const uint32_t abuf = two_deep ? (sidx & 1u) : 0u;
+                    const uint32_t ta = tmem_a0 + (abuf * kKT + (uint32_t)group) * 32 + ((uint32_t)(quad * 32) << 16);
+                    if (fr) {
+                        tc_fence_after();
+                        tc_st_32x32b_x16(ta, a);
+                    }
+                    // ---- pass 2, second half
+#if !defined(SPB_EXP_NO_PASS2) && !defined(SPB_EXP_NO_DECODE)
+#pragma unroll
+                    for (int q = 4; q < 8; ++q) decode_unit(m0[q], m1[q], lut, a + 4 * q);
+#endif
+                    if (fr) {
+                        tc_st_32x32b_x16(ta + 16, a + 16);
+                        tc_wait_st();
+                        tc_fence_before();
+                    }
+                    ok = fr;
                 }
                 __syncwarp();
-                if (lane == 0) {
-                    if (fr) mbar_arrive(bar_aready + 8 * abuf);
+                if (lane == 0 && ok) {
+                    mbar_arrive(bar_aready + 8 * (two_deep ? (sidx & 1u) : 0u));
                     mbar_arrive(bar_empty + 8 * slot);
                 }
-                ok = fr;
                 bar_old = bar_new;
                 par_old = par_new;
                 bar_new = bar_empty + 8 * slot;
                 par_new = round & 1;
-                ++mine;
-                slot += kDecodeGroups;
-                if (slot >= (uint32_t)S) {
-                    slot -= (uint32_t)S;
+                if (++slot == (uint32_t)S) {
+                    slot = 0;
                     ++round;
                 }
-                abuf += kDecodeGroups;
-                if (abuf >= n_abufs) abuf -= n_abufs;
-                SPB_T(t6);
-                SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(2, t3 - t2); SPB_ACC(3, t4 - t3);
-                SPB_ACC(4, t5 - t4); SPB_ACC(5, t6 - t5); SPB_ACC(6, 1);
+                SPB_T(t2);
+                SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
                 if (!ok) break;
-            }
-            // first k-tile of the next item that belongs to this group
-            if (ok) {
-                const int rem = (w.nk - skip) % kDecodeGroups;
-                skip = w.nk <= skip ? skip - w.nk : (rem == 0 ? 0 : kDecodeGroups - rem);
             }
         }
 #ifdef SPB_TIMING
-        if (blockIdx.x == 0 && lane == 0)
-            printf("decode warp %d: n=%lld wait_full=%lld pass1=%lld sync=%lld pass2a=%lld wait_afree=%lld rest=%lld (avg clk)\n",
-                   dw, tacc[6], tacc[0] / tacc[6], tacc[1] / tacc[6], tacc[2] / tacc[6], tacc[3] / tacc[6],
-                   tacc[4] / tacc[6], tacc[5] / tacc[6]);
+        if (blockIdx.x == 0 && lane == 0 && (dw % 5) == 0)
+            printf("decode warp %d: stages=%lld wait_full=%lld work=%lld\n", dw, tacc[6], tacc[0] / tacc[6], tacc[1] / tacc[6]);
 #endif
     }
 
@@ -908,10 +989,11 @@ cudaError_t spmm_launch(cudaStream_t s, const SpmmArgs& a)
     int* status = nullptr;
     cudaError_t e = device_status_ptr(&status);
     if (e != cudaSuccess) return e;
+    // Activation tile width: the smallest of 16/32/64 that holds N; wider N is cut into tiles of 64
+    // columns (each re-reads and re-expands the weight).
     if (a.N <= 16) return launch_t<16>(s, a, di, status);
     if (a.N <= 32) return launch_t<32>(s, a, di, status);
-    if (a.N <= 64) return launch_t<64>(s, a, di, status);
-    return launch_t<128>(s, a, di, status);
+    return launch_t<64>(s, a, di, status);
 }
 
 }  // namespace spb
