@@ -809,6 +809,17 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         tc_fence_before();
                     }
                     ok = fr;
+                } else {
+                    // A group without a k-tile in this stage still arrives on aready.  Arrivals are
+                    // not tagged with a phase, so it must not run ahead of the stage two back either:
+                    // an early arrival would complete that stage's aready phase in place of a warp
+                    // that is still decoding.
+                    if (two_deep) {
+                        if (sidx >= 2) ok = mbar_wait(bar_old, par_old, abort_flag);
+                    } else if (sidx >= 1) {
+                        ok = mbar_wait(bar_new, par_new, abort_flag);
+                    }
+                    ok = __all_sync(0xffffffffu, ok);
                 }
                 __syncwarp();
                 if (lane == 0 && ok) {

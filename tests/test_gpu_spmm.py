@@ -67,6 +67,16 @@ def test_spmm_matches_fp32_oracle(sp, M, K, N, s, sk):
     assert sp.device_status() == 0
 
 
+def test_many_short_work_items_per_sm(sp):
+    """300 row blocks of 5 k-tiles: every SM runs several work items whose last pipeline stage is partly empty."""
+    M, K, N = 128 * 300, 64 * 5, 16
+    A = make_sparse(M, K, 0.5, seed=31)
+    B = make_dense(N, K, seed=32)
+    for sk in (1, 2):
+        _assert_close(_run(sp, A, B, sk), oracle.gemm_f32(A, B))
+    assert sp.device_status() == 0
+
+
 def test_spmm_from_reference_format_host_arrays(sp):
     """Arrays produced by the reference-format host encoder, uploaded as FT's loader would, max_nnz rounded to 64."""
     A = make_sparse(384, 640, 0.6, seed=77)
