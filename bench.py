@@ -219,7 +219,7 @@ def main():
             i, N = k
             sp.spmm(mats[i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
             if world > 1:
-                dist.all_gather(list(gathered[k].unbind(0)), outs[k])
+                dist.all_gather_into_tensor(gathered[k], outs[k])
 
     def sync_all():
         torch.cuda.synchronize()
@@ -260,7 +260,7 @@ def main():
             acts[k].copy_(h_acts[k], non_blocking=True)
             sp.spmm(mats[i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
             if world > 1:
-                dist.all_gather(list(gathered[k].unbind(0)), outs[k])
+                dist.all_gather_into_tensor(gathered[k], outs[k])
                 d_full[k].copy_(gathered[k].permute(1, 0, 2).reshape(N, -1))
                 h_outs[k].copy_(d_full[k], non_blocking=True)
             else:

@@ -36,8 +36,17 @@ namespace {
 //   warpgroup 0: warp 1 MMA issuer, warps 0, 2, 3 producers (each issues a share of the copies)
 //   warpgroup 1: epilogue (one warp per TMEM lane quadrant)
 //   warpgroup 2..: decode groups (one warp per quadrant each)
-constexpr int kKT = 4;                // k-tiles per pipeline stage == decode groups
-constexpr int kDecodeGroups = kKT;
+#ifndef SPB_KT
+#define SPB_KT 4
+#endif
+// A pipeline stage holds kKT consecutive k-tiles of one 128-row block.  The four decode groups are
+// split into kSets sets of kKT groups; set s expands the stages s, s + kSets, ..., one group per k-tile.
+// Smaller stages mean more stages in the shared-memory ring (the loop producer -> HBM -> decode ->
+// MMA -> release is latency-bound), larger ones mean fewer copies per byte.
+constexpr int kKT = SPB_KT;
+constexpr int kDecodeGroups = 4;
+constexpr int kSets = kDecodeGroups / kKT;
+static_assert(kKT * kSets == kDecodeGroups, "kKT must be 1, 2 or 4");
 constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
@@ -46,9 +55,13 @@ constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kDecodeGroups);
 // Registers per thread after the roles have resized (the launch gives every thread
 // 65536 / kThreads rounded down to a multiple of 8).
 constexpr int kRegsControl = 40, kRegsEpilogue = 56, kRegsDecode = 96;
-static_assert(128 * kRegsControl + 128 * kRegsEpilogue + 128 * kDecodeGroups * kRegsDecode <= 65536 - 2048,
-              "register budget (keep slack: a resize that can never be satisfied would block forever)");
-constexpr int kMaxStages = 8;
+// The register file is handed out per warp in blocks of 512 registers (16 per thread), so the budget
+// is checked on rounded-up sizes; a resize that cannot be satisfied blocks the warp for ever.
+constexpr int regs_rounded(int r) { return (r + 15) / 16 * 16; }
+static_assert(128 * regs_rounded(kRegsControl) + 128 * regs_rounded(kRegsEpilogue) +
+                      128 * kDecodeGroups * regs_rounded(kRegsDecode) <= 65536 - 2048,
+              "register budget (keep slack: a resize that can never be satisfied would block for ever)");
+constexpr int kMaxStages = 24;
 // Per-row metadata of one stage, 8 bytes per (tile, row):
 //   word 0  shared-memory byte address of the row's first packed value
 //   word 1  byte 0: 8 * low nibble of the row mask, byte 1: 8 * high nibble (offsets into the
@@ -71,6 +84,13 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 #define SPB_TDECL
 #define SPB_T(x)
 #define SPB_ACC(i, v)
+#endif
+
+#ifdef SPB_TIMELINE
+__device__ long long g_tl[96][8];
+#define SPB_TL(stage, col) do { if (blockIdx.x == 0 && lane == 0 && (stage) < 96) g_tl[(stage)][(col)] = clock64(); } while (0)
+#else
+#define SPB_TL(stage, col)
 #endif
 
 struct KernelParams {
@@ -123,6 +143,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (i > 64) {
             if (*abort_flag) return false;
             __nanosleep(40);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+// Same, for the control warps, which spend most of their time waiting for the decode warps: after a
+// few quick tries they sleep between polls so that their polling does not take issue slots and
+// integer-pipe cycles from the decode warps of the same scheduler.
+__device__ __forceinline__ bool mbar_wait_patient(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (i >= 4) {
+            if (*abort_flag) return false;
+            __nanosleep(150);
         }
     }
     *abort_flag = 1;
@@ -336,24 +371,35 @@ __device__ __forceinline__ uint2 lut_high_entry(uint32_t n)
     return make_uint2(pair_sel_top(b6, b7) | (win << 16), pair_sel_top(b4, b5));
 }
 
-// Expand one 8-element row segment described by its two metadata words into 4 registers of packed
-// fp16.  lut: shared address of the selector tables (a link-time constant).
-__device__ __forceinline__ void decode_unit(uint32_t w0, uint32_t w1, uint32_t lut, uint32_t* o)
+// Expansion of one 8-element row segment described by its two metadata words into 4 registers of
+// packed fp16, split into a load half and a compute half so that the loads of several segments can
+// be in flight together.  lut: shared address of the selector tables (a link-time constant).
+#ifndef SPB_UNIT_BATCH
+#define SPB_UNIT_BATCH 1
+#endif
+constexpr int kUnitBatch = SPB_UNIT_BATCH;  // row segments whose loads are issued together (1, 2 or 4)
+struct UnitLoads {
+    uint32_t x0, x1, x2, y0, y1, y2, l0, l1, h0, h1, sb, st;
+};
+__device__ __forceinline__ void unit_load(uint32_t w0, uint32_t w1, uint32_t lut, UnitLoads& u)
 {
     const uint32_t ilo = prmt(w1, 0u, 0x4440u), ihi = prmt(w1, 0u, 0x4441u), k2 = prmt(w1, 0u, 0x4442u);
-    uint32_t x0, x1, x2, y0, y1, y2, l0, l1, h0, h1;
-    lds32x3(w0 & ~3u, x0, x1, x2);
+    lds32x3(w0 & ~3u, u.x0, u.x1, u.x2);
     const uint32_t wt = w0 + k2 - 8u;  // address of the value 4 before the row's end
-    lds32x3(wt & ~3u, y0, y1, y2);
-    lds64(lut + ilo, l0, l1);
-    lds64(lut + 128u + ihi, h0, h1);
-    const uint32_t sb = w0 << 3, st = wt << 3;  // funnel shifts use the low 5 bits: 0 or 16
-    const uint32_t b0 = __funnelshift_r(x0, x1, sb), b1 = __funnelshift_r(x1, x2, sb);
-    const uint32_t t0 = __funnelshift_r(y0, y1, st), t1 = __funnelshift_r(y1, y2, st);
-    o[0] = prmt(b0, 0u, l0);
-    o[1] = prmt(prmt(b0, b1, l0 >> 16), 0u, l1);
-    o[2] = prmt(prmt(t0, t1, h0 >> 16), 0u, h1);
-    o[3] = prmt(t1, 0u, h0);
+    lds32x3(wt & ~3u, u.y0, u.y1, u.y2);
+    lds64(lut + ilo, u.l0, u.l1);
+    lds64(lut + 128u + ihi, u.h0, u.h1);
+    u.sb = w0 << 3;  // funnel shifts use the low 5 bits: 0 or 16
+    u.st = wt << 3;
+}
+__device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
+{
+    const uint32_t b0 = __funnelshift_r(u.x0, u.x1, u.sb), b1 = __funnelshift_r(u.x1, u.x2, u.sb);
+    const uint32_t t0 = __funnelshift_r(u.y0, u.y1, u.st), t1 = __funnelshift_r(u.y1, u.y2, u.st);
+    o[0] = prmt(b0, 0u, u.l0);
+    o[1] = prmt(prmt(b0, b1, u.l0 >> 16), 0u, u.l1);
+    o[2] = prmt(prmt(t0, t1, u.h0 >> 16), 0u, u.h1);
+    o[3] = prmt(t1, 0u, u.h0);
 }
 
 template <int NPAD>
@@ -389,10 +435,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t bar_full = smem_u32(bars);                         // [kMaxStages]
     const uint32_t bar_empty = bar_full + 8 * kMaxStages;             // [kMaxStages]
-    const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [2]
-    const uint32_t bar_accfull = bar_aready + 16;                     // [2]
+    const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [2 * kSets]
+    const uint32_t bar_accfull = bar_aready + 8 * 2 * kSets;          // [2]
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 6));
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kSets + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     uint8_t* meta_base = smem + kHeaderBytes;
     const uint32_t stage0 = smem_u32(smem + kHeaderBytes + kMetaBytes);
@@ -403,7 +449,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     constexpr int kNAcc = 4;
     constexpr int kAccBufs = NPAD <= 32 ? 2 : 1;
     constexpr uint32_t kAccCols = kAccBufs * kNAcc * NPAD;
-    constexpr uint32_t kACols = 2 * kKT * 32;  // two stages' worth of A operands
+    constexpr uint32_t kACols = 2 * kSets * kKT * 32;  // A operands of two stages per set
     static_assert(kAccCols + kACols <= 512, "TMEM budget");
     constexpr uint32_t kTmemCols = 512;
 
@@ -412,8 +458,8 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             mbar_init(bar_full + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, 4 * kKT + 1);  // every decode warp + the MMA commit
         }
+        for (int i = 0; i < 2 * kSets; ++i) mbar_init(bar_aready + 8 * i, 4 * kKT);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar_aready + 8 * i, 4 * kKT);
             mbar_init(bar_accfull + 8 * i, 1);
             mbar_init(bar_accempty + 8 * i, 4);
         }
@@ -436,9 +482,13 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t tmem_base = *tmem_holder;
     const uint32_t tmem_a0 = tmem_base + kAccCols;
 
-    // With three or more stages the A operands in TMEM are double-buffered per stage (a decode warp
-    // may overwrite a buffer once the MMAs of the stage two back have completed); otherwise single.
-    const bool two_deep = S >= 3;
+    // The A operands of n_abuf stages live in TMEM: two per set when the ring is deep enough, else one.
+    // A decode warp may overwrite a buffer once the MMAs of the stage n_abuf back have completed, which
+    // it learns from that stage's empty barrier; with a ring no deeper than n_abuf the full barrier of
+    // its own stage already implies it.
+    const uint32_t n_abuf = S > 2 * kSets ? 2u * kSets : (uint32_t)kSets;
+    const bool reuse_wait = (uint32_t)S > n_abuf;
+    const bool two_deep = n_abuf == 2u * kSets;
     if (S < 1) {
         // A single stage does not fit (cannot happen with the launch configuration used by the host
         // code); leave cleanly.
@@ -453,56 +503,87 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             //   warp 2  copies bitmaps and median offsets
             //   warp 3  loads the activation tiles
             const int prole = warp == 0 ? 0 : warp - 1;
-            // The global-tile offsets of a stage are fetched one stage ahead, so that their latency
-            // overlaps with the wait for a free stage and the issue of the previous copies.
-            auto fetch_offsets = [&](const Item& w, int kk0) -> int {
-                const int nv = min(kKT, w.nk - kk0);
-                const size_t g0 = (size_t)(2 * w.y) * p.kt_total + w.k0 + kk0;
-                const bool chunk1 = (2 * w.y + 1) < p.gm_total;
-                // lanes 0..nv: offsets of row 0's tiles; lanes 8..8+nv: row 1's
-                int v = 0;
-                if (lane <= nv) v = __ldg(p.gtile + g0 + lane);
-                if (chunk1 && lane >= 8 && lane - 8 <= nv) v = __ldg(p.gtile + g0 + p.kt_total + (lane - 8));
-                return v;
+            // Global-tile offsets are read in batches of 32 consecutive k-tiles (lane l holds the offset of
+            // k-tile base + l of both 64-row global-tile rows) and one batch ahead, so that the latency of
+            // these loads never sits between two stages.
+            constexpr int kOffBatch = 28;  // k-tiles a batch advances by; a stage needs up to base + 27 + kKT
+            struct Batch {
+                int item, base, v0, v1;
+                Item w;
+            };
+            auto load_batch = [&](Batch& b) {
+                b.v0 = 0;
+                b.v1 = 0;
+                if (prole != 0 || b.item >= p.num_items) return;
+                const size_t g = (size_t)(2 * b.w.y) * p.kt_total + b.w.k0 + b.base;
+                if (lane <= b.w.nk - b.base) {
+                    b.v0 = __ldg(p.gtile + g + lane);
+                    if ((2 * b.w.y + 1) < p.gm_total) b.v1 = __ldg(p.gtile + g + p.kt_total + lane);
+                }
+            };
+            auto next_nonempty = [&](int it, Item& w) -> int {
+                do {
+                    it += gridDim.x;
+                    if (it < p.num_items) w = decode_item(p, it);
+                } while (it < p.num_items && w.nk == 0);
+                return it;
+            };
+            auto batch_after = [&](const Batch& b) -> Batch {
+                Batch n = b;
+                if (b.base + kOffBatch < b.w.nk) {
+                    n.base = b.base + kOffBatch;
+                } else {
+                    n.base = 0;
+                    n.item = next_nonempty(b.item, n.w);
+                }
+                return n;
             };
             uint32_t slot = 0, round = 0;
             bool ok = true;
             SPB_TDECL;
+            int tl_stage = 0;
             int item = blockIdx.x, kk0 = 0;
             Item w = decode_item(p, item < p.num_items ? item : 0);
-            while (item < p.num_items && w.nk == 0) {  // skip empty split-K ranges
-                item += gridDim.x;
-                if (item < p.num_items) w = decode_item(p, item);
-            }
-            int myoff = (prole == 0 && item < p.num_items) ? fetch_offsets(w, 0) : 0;
+            if (item < p.num_items && w.nk == 0) item = next_nonempty(item, w);
+            Batch cur;
+            cur.item = item;
+            cur.base = 0;
+            cur.w = w;
+            load_batch(cur);
+            Batch nxt = batch_after(cur);
+            load_batch(nxt);
             while (item < p.num_items && ok) {
                 const Item cw = w;
                 const int ckk0 = kk0;
-                const int cur_off = myoff;
-                // advance to the next stage and start fetching its offsets
+                if (cur.item != item || ckk0 - cur.base >= kOffBatch) {  // this stage starts the next batch
+                    cur = nxt;
+                    nxt = batch_after(cur);
+                    load_batch(nxt);
+                }
+                const int bidx = ckk0 - cur.base;
+                // advance to the next stage
                 kk0 += kKT;
                 if (kk0 >= w.nk) {
                     kk0 = 0;
-                    do {
-                        item += gridDim.x;
-                        if (item < p.num_items) w = decode_item(p, item);
-                    } while (item < p.num_items && w.nk == 0);
+                    item = next_nonempty(item, w);
                 }
-                if (prole == 0 && item < p.num_items) myoff = fetch_offsets(w, kk0);
 
                 const bool chunk1 = (2 * cw.y + 1) < p.gm_total;
                 const int nv = min(kKT, cw.nk - ckk0);
                 const size_t g0 = (size_t)(2 * cw.y) * p.kt_total + cw.k0 + ckk0;
-                const int a0 = __shfl_sync(0xffffffffu, cur_off, 0), e0 = __shfl_sync(0xffffffffu, cur_off, nv);
-                const int a1 = __shfl_sync(0xffffffffu, cur_off, 8), e1 = __shfl_sync(0xffffffffu, cur_off, 8 + nv);
+                const int a0 = __shfl_sync(0xffffffffu, cur.v0, bidx), e0 = __shfl_sync(0xffffffffu, cur.v0, bidx + nv);
+                const int a1 = __shfl_sync(0xffffffffu, cur.v1, bidx), e1 = __shfl_sync(0xffffffffu, cur.v1, bidx + nv);
+                const int r0 = __shfl_sync(0xffffffffu, cur.v0, bidx + (lane & 7));
+                const int r1 = __shfl_sync(0xffffffffu, cur.v1, bidx + (lane & 7));
                 SPB_T(t0);
-                if (round > 0) ok = mbar_wait(bar_empty + 8 * slot, (round - 1) & 1, abort_flag);
+                if (round > 0) ok = mbar_wait_patient(bar_empty + 8 * slot, (round - 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 SPB_T(t1);
+                if (prole == 0) SPB_TL(tl_stage, 0);
                 uint32_t n0 = (uint32_t)(e0 - a0) * 2, n1 = chunk1 ? (uint32_t)(e1 - a1) * 2 : 0u;
                 if (e0 < a0 || n0 > (uint32_t)nv * vmax || (chunk1 && (e1 < a1 || n1 > (uint32_t)nv * vmax))) {
-                    if (lane == 0) atomicOr(p.status, (int)kStatusBadOffsets);
+                    if (lane == 0 && prole == 0) atomicOr(p.status, (int)kStatusBadOffsets);
                     n0 = 0;
                     n1 = 0;
                 }
@@ -511,7 +592,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 // where each global tile's values start inside the run (clamped: corrupt offsets must
                 // not lead the decode warps outside the stage)
                 if (prole == 0 && (lane < kKT || (lane >= 8 && lane < 8 + kKT))) {
-                    const uint32_t rel = (uint32_t)(cur_off - (lane < 8 ? a0 : a1)) * 2;
+                    const uint32_t rel = (uint32_t)(lane < 8 ? r0 - a0 : r1 - a1) * 2;
                     const uint32_t idx = lane < 8 ? (uint32_t)lane : (uint32_t)(kKT + lane - 8);
                     asm volatile("st.shared.b32 [%0], %1;" ::"r"(sbase + off_rel + 4 * idx),
                                  "r"(min(rel, (uint32_t)kKT * vmax))
@@ -540,6 +621,8 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     }
                 }
                 __syncwarp();
+                SPB_TL(tl_stage, 1 + prole);
+                ++tl_stage;
                 SPB_T(t2);
                 SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
                 if (++slot == (uint32_t)S) {
@@ -561,8 +644,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             // its empty barrier: the producer may refill the stage and the decode warps may
             // overwrite the TMEM A buffers.
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            uint32_t idx = 0, slot = 0, sidx = 0;
+            uint32_t idx = 0, slot = 0, abuf = 0, apar = 0;
             bool ok = true;
+            int tl_stage = 0;
             SPB_TDECL;
             for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
                 const Item w = decode_item(p, item);
@@ -570,16 +654,15 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 const uint32_t accbuf = idx % kAccBufs;
                 if (idx >= (uint32_t)kAccBufs)
                     ok = __all_sync(0xffffffffu,
-                                    mbar_wait(bar_accempty + 8 * accbuf, ((idx / kAccBufs) - 1) & 1, abort_flag));
+                                    mbar_wait_patient(bar_accempty + 8 * accbuf, ((idx / kAccBufs) - 1) & 1, abort_flag));
                 const uint32_t d_tmem = tmem_base + accbuf * (kNAcc * NPAD);
-                for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT, ++sidx) {
+                for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT) {
                     const int nv = min(kKT, w.nk - kk0);
-                    const uint32_t abuf = two_deep ? (sidx & 1u) : 0u;
-                    const uint32_t apar = two_deep ? ((sidx >> 1) & 1u) : (sidx & 1u);
                     SPB_T(t0);
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_aready + 8 * abuf, apar, abort_flag));
+                    ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_aready + 8 * abuf, apar, abort_flag));
                     if (!ok) break;
                     SPB_T(t1);
+                    SPB_TL(tl_stage, 6);
                     tc_fence_after();
                     const uint32_t sbase = stage0 + slot * stage_bytes;
                     if (elect_one()) {
@@ -594,9 +677,15 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         tc_commit(bar_empty + 8 * slot);
                     }
                     __syncwarp();
+                    SPB_TL(tl_stage, 7);
+                    ++tl_stage;
                     SPB_T(t2);
                     SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
                     if (++slot == (uint32_t)S) slot = 0;
+                    if (++abuf == n_abuf) {
+                        abuf = 0;
+                        apar ^= 1u;
+                    }
                 }
                 if (ok && elect_one()) tc_commit(bar_accfull + 8 * accbuf);
                 __syncwarp();
@@ -660,25 +749,27 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
     } else {
         // ================================================================= decode
-        // Decode group g (4 warps, one per TMEM lane quadrant) expands k-tile g of every stage.
+        // Decode group g (4 warps, one per TMEM lane quadrant) belongs to set g / kKT and expands k-tile
+        // g % kKT of every stage of its set.
         // Every warp works alone: the 32 weight rows of its quadrant cross exactly the 32 bitmap
         // tiles 32*quad .. 32*quad+31 of the k-tile, so the tile metadata a warp needs in pass 2 is
         // the metadata its own lanes produce in pass 1.
         reg_alloc<kRegsDecode>();
         const int dw = warp - kDecodeWarp0;
         const int group = dw >> 2;
+        const int set = group / kKT, sub = group % kKT;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;      // weight row inside the 128-row block == tile index in pass 1
         const uint32_t meta = smem_u32(meta_base + group * kMetaBufBytes);
-        uint8_t* cnt_s = meta_base + kKT * kMetaBufBytes + dw * 32;  // 32 tile counts of this warp
+        uint8_t* cnt_s = meta_base + kDecodeGroups * kMetaBufBytes + dw * 32;  // 32 tile counts of this warp
         const uint32_t lut = smem_u32(lut_tab);
         // pass 1: this thread owns tile `row` of the k-tile (tile t of global-tile row t>>6)
         const int chunk = row >> 6, rr = row & 63;
         const uint32_t p1_addr = meta + (uint32_t)row * 16;
         const uint32_t my_v = chunk ? off_v1 : off_v0;
-        const uint32_t my_bm = (chunk ? off_bm1 : off_bm0) + (uint32_t)group * 512 + 8 * (uint32_t)rr;
-        const uint32_t my_mt = (chunk ? off_mt1 : off_mt0) + (uint32_t)group * 16 + 4 * (uint32_t)(rr >> 4);
-        const uint32_t my_rel = off_rel + 4 * (uint32_t)(chunk * kKT + group);
+        const uint32_t my_bm = (chunk ? off_bm1 : off_bm0) + (uint32_t)sub * 512 + 8 * (uint32_t)rr;
+        const uint32_t my_mt = (chunk ? off_mt1 : off_mt0) + (uint32_t)sub * 16 + 4 * (uint32_t)(rr >> 4);
+        const uint32_t my_rel = off_rel + 4 * (uint32_t)(chunk * kKT + sub);
         // byte masks selecting, in the 16 counts of this lane's median tile, the tiles before its own
         uint32_t before[4];
 #pragma unroll
@@ -692,21 +783,34 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         const uint32_t maddr = meta + (uint32_t)(r_in_tile >> 1) * kMetaPieceBytes + (uint32_t)tbase * 16 +
                                (uint32_t)(r_in_tile & 1) * 8;
 
-        uint32_t slot = 0, round = 0, sidx = 0;
-        uint32_t bar_old = 0, par_old = 0, bar_new = 0, par_new = 0;  // empty barriers of the last two stages
+        uint32_t slot = 0, round = 0, mine = 0;
+        int tl_stage = 0;
+        int turn = 0;      // stage counter modulo kSets: this warp's set works when turn == set
+        uint32_t abuf = (uint32_t)set;  // TMEM A buffer (in stages) of this set's next stage
+        uint32_t bar_old = 0, par_old = 0, bar_new = 0, par_new = 0;  // empty barriers of this set's last two stages
         bool ok = true;
         SPB_TDECL;
         for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
             const Item w = decode_item(p, item);
             const bool chunk1 = (2 * w.y + 1) < p.gm_total;
             const bool valid = (chunk == 0) || chunk1;
-            for (int kk0 = 0; kk0 < w.nk; kk0 += kKT, ++sidx) {
-                const bool active = group < w.nk - kk0;  // this group's k-tile exists in the stage
+            for (int kk0 = 0; kk0 < w.nk; kk0 += kKT) {
+                if (turn != set) {  // another set's stage: only follow the ring
+                    ++tl_stage;
+                    if (++turn == kSets) turn = 0;
+                    if (++slot == (uint32_t)S) {
+                        slot = 0;
+                        ++round;
+                    }
+                    continue;
+                }
+                const bool active = sub < w.nk - kk0;  // this group's k-tile exists in the stage
                 SPB_T(t0);
                 ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 SPB_T(t1);
+                if (sub == 0 && quad == 0) SPB_TL(tl_stage, 4);
                 const uint32_t st = stage0 + slot * stage_bytes;
                 uint32_t a[32];
                 if (active) {
@@ -781,19 +885,26 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
 #pragma unroll
                     for (int q = 0; q < 8; ++q) lds64(maddr + 32 * q, m0[q], m1[q]);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) decode_unit(m0[q], m1[q], lut, a + 4 * q);
+                    for (int q0 = 0; q0 < 4; q0 += kUnitBatch) {
+                        UnitLoads u[kUnitBatch];
+#pragma unroll
+                        for (int q = 0; q < kUnitBatch; ++q) unit_load(m0[q0 + q], m1[q0 + q], lut, u[q]);
+#pragma unroll
+                        for (int q = 0; q < kUnitBatch; ++q) unit_expand(u[q], a + 4 * (q0 + q));
+                    }
 #endif
 #endif
                     // the TMEM A buffer may be rewritten once the MMAs that read it have completed
                     bool fr = true;
-                    if (two_deep) {
-                        if (sidx >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
-                    } else if (sidx >= 1) {
-                        fr = mbar_wait(bar_new, par_new, abort_flag);
+                    if (reuse_wait) {
+                        if (two_deep) {
+                            if (mine >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
+                        } else if (mine >= 1) {
+                            fr = mbar_wait(bar_new, par_new, abort_flag);
+                        }
                     }
                     fr = __all_sync(0xffffffffu, fr);
-                    const uint32_t abuf = two_deep ? (sidx & 1u) : 0u;
-                    const uint32_t ta = tmem_a0 + (abuf * kKT + (uint32_t)group) * 32 + ((uint32_t)(quad * 32) << 16);
+                    const uint32_t ta = tmem_a0 + (abuf * kKT + (uint32_t)sub) * 32 + ((uint32_t)(quad * 32) << 16);
                     if (fr) {
                         tc_fence_after();
                         tc_st_32x32b_x16(ta, a);
@@ -801,7 +912,13 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     // ---- pass 2, second half
 #if !defined(SPB_EXP_NO_PASS2) && !defined(SPB_EXP_NO_DECODE)
 #pragma unroll
-                    for (int q = 4; q < 8; ++q) decode_unit(m0[q], m1[q], lut, a + 4 * q);
+                    for (int q0 = 4; q0 < 8; q0 += kUnitBatch) {
+                        UnitLoads u[kUnitBatch];
+#pragma unroll
+                        for (int q = 0; q < kUnitBatch; ++q) unit_load(m0[q0 + q], m1[q0 + q], lut, u[q]);
+#pragma unroll
+                        for (int q = 0; q < kUnitBatch; ++q) unit_expand(u[q], a + 4 * (q0 + q));
+                    }
 #endif
                     if (fr) {
                         tc_st_32x32b_x16(ta + 16, a + 16);
@@ -814,22 +931,30 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     // not tagged with a phase, so it must not run ahead of the stage two back either:
                     // an early arrival would complete that stage's aready phase in place of a warp
                     // that is still decoding.
-                    if (two_deep) {
-                        if (sidx >= 2) ok = mbar_wait(bar_old, par_old, abort_flag);
-                    } else if (sidx >= 1) {
-                        ok = mbar_wait(bar_new, par_new, abort_flag);
+                    if (reuse_wait) {
+                        if (two_deep) {
+                            if (mine >= 2) ok = mbar_wait(bar_old, par_old, abort_flag);
+                        } else if (mine >= 1) {
+                            ok = mbar_wait(bar_new, par_new, abort_flag);
+                        }
                     }
                     ok = __all_sync(0xffffffffu, ok);
                 }
                 __syncwarp();
                 if (lane == 0 && ok) {
-                    mbar_arrive(bar_aready + 8 * (two_deep ? (sidx & 1u) : 0u));
+                    mbar_arrive(bar_aready + 8 * abuf);
                     mbar_arrive(bar_empty + 8 * slot);
                 }
+                if (sub == 0 && quad == 0) SPB_TL(tl_stage, 5);
+                ++tl_stage;
                 bar_old = bar_new;
                 par_old = par_new;
                 bar_new = bar_empty + 8 * slot;
                 par_new = round & 1;
+                ++mine;
+                abuf += kSets;
+                if (abuf >= n_abuf) abuf -= n_abuf;
+                if (++turn == kSets) turn = 0;
                 if (++slot == (uint32_t)S) {
                     slot = 0;
                     ++round;
@@ -860,6 +985,15 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
         __syncthreads();
     }
+#ifdef SPB_TIMELINE
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        const long long t00 = g_tl[0][0];
+        printf("stage: prod_go p0_done p1_done p2_done | dec_got dec_done | mma_go mma_done  (clk, S=%d)\n", S);
+        for (int i = 0; i < 40; ++i)
+            printf("%3d: %7lld %7lld %7lld %7lld | %7lld %7lld | %7lld %7lld\n", i, g_tl[i][0] - t00, g_tl[i][1] - t00,
+                   g_tl[i][2] - t00, g_tl[i][3] - t00, g_tl[i][4] - t00, g_tl[i][5] - t00, g_tl[i][6] - t00, g_tl[i][7] - t00);
+    }
+#endif
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }

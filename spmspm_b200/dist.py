@@ -33,7 +33,10 @@ def all_gather_rows(local_C, group=None):
         return local_C
     N, Ms = local_C.shape
     buf = torch.empty((world, N, Ms), dtype=local_C.dtype, device=local_C.device)
-    dist.all_gather(list(buf.unbind(0)), local_C.contiguous(), group=group)
+    if local_C.is_cuda:
+        dist.all_gather_into_tensor(buf, local_C.contiguous(), group=group)
+    else:  # gloo has no flat-tensor variant
+        dist.all_gather(list(buf.unbind(0)), local_C.contiguous(), group=group)
     return buf.permute(1, 0, 2).reshape(N, world * Ms)
 
 
