@@ -109,6 +109,29 @@ int spb_spmm_bitmap_v3(void* stream, const uint16_t* A, const uint16_t* Compress
                        uint16_t* Reduction_Workspace, int Split_K);
 
 /*
+ * The same SpMM for callers that can neither pass a reduction workspace nor let the library allocate
+ * one (no counterpart in the reference, whose callers always bring their own workspace).  Typical
+ * callers: a serving process that fixes its device-memory plan at start-up and bans allocation while
+ * requests run, a plug-in that is only given the framework's input and output tensors, code executing
+ * during stream capture.  The fp16 split-K partials go to an array of
+ * SPB_NOALLOC_MAX_SCRATCH_BYTES that is part of the library's device image (each GPU that loads the
+ * library holds it until the process ends).  The call performs no cudaMalloc/cudaFree and uses no
+ * allocating library routine.
+ *   - Split_K*M*N*2 bytes must fit the array; larger requests fail with cudaErrorInvalidValue and
+ *     launch nothing.  Split_K == 1 needs no scratch and has no size limit.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+ *     prepares the kernel; make that first call outside any stream capture.
+ *   - All calls share the one array and it keeps whatever the previous call left; the kernels
+ *     overwrite every partial they later read, so no clearing is needed, but two calls whose
+ *     kernels overlap on the GPU (different streams) race on it: serialise them.
+ * Arguments as spb_spmm_bitmap_v3 without A and Reduction_Workspace.
+ */
+#define SPB_NOALLOC_MAX_SCRATCH_BYTES (16u << 20)
+int spb_spmm_bitmap_v3_noalloc(void* stream, const uint16_t* Compressed_A, const int* TileOffsets,
+                               const int* TileOffsets_Median, const uint64_t* bitmap, const int* max_nnz_intile,
+                               const uint16_t* B, uint16_t* C, int M_Global, int N_Global, int K_Global, int Split_K);
+
+/*
  * Split-K reduction alone.  Replaces the SplitK_Reduction launch
  * (csrc/SpMM_API.cuh:106-108, csrc/Reduction_Kernel.cuh:24-44).
  */

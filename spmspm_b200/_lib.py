@@ -28,6 +28,8 @@ SIGNATURES = {
     "spb_gen_bin_files": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_char_p] * 6),
     "spb_spmm_bitmap_v3": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,
                                           ctypes.c_int, _vp, ctypes.c_int]),
+    "spb_spmm_bitmap_v3_noalloc": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,
+                                                  ctypes.c_int, ctypes.c_int]),
     "spb_splitk_reduce": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "spb_suggest_split_k": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "spb_device_status": (ctypes.c_int, [_i32p]),
@@ -39,6 +41,8 @@ MANGLED = [
     "_Z25SpMM_SplitK_API_bitmap_v3P11CUstream_stPK6__halfS3_PKiS5_PKmS5_S3_PS1_iiiS8_i",
     "_Z24InitSparseMatrixA_bitmapP6__halfiiiiiiiiPS0_PPiS3_S3_PPmRi",
 ]
+
+NOALLOC_MAX_SCRATCH_BYTES = 16 << 20  # SPB_NOALLOC_MAX_SCRATCH_BYTES in include/spmm_b200.h
 
 _lib = None
 

@@ -222,6 +222,21 @@ def spmm(W: BitmapMatrix, B, split_k=None, out=None, workspace=None, stream=None
     return out
 
 
+def spmm_noalloc(W: BitmapMatrix, B, split_k, out, stream=None):
+    """spb_spmm_bitmap_v3_noalloc: split-K SpMM whose partial sums use the library's built-in scratch array.
+
+    For callers that must not allocate device memory: `out` has to be supplied, nothing is allocated here or in
+    the library.  Raises SpmmError when split_k * M * N * 2 bytes exceed the built-in array.
+    """
+    N = B.shape[0]
+    with torch.cuda.device(B.device):
+        code = _lib.load().spb_spmm_bitmap_v3_noalloc(_stream_ptr(stream), _ptr(W.vals), _ptr(W.gtile), _ptr(W.mtile),
+                                                      _ptr(W.bitmap), _ptr(W.max_nnz), _ptr(B), _ptr(out), W.M, N, W.K,
+                                                      split_k)
+    _check(code, "spb_spmm_bitmap_v3_noalloc")
+    return out
+
+
 def splitk_reduce(C, workspace, M, N, split_k, stream=None):
     _check(_lib.load().spb_splitk_reduce(_stream_ptr(stream), _ptr(C), _ptr(workspace), M, N, split_k),
            "spb_splitk_reduce")
