@@ -302,6 +302,12 @@ def main():
                      "note": "algorithmic bytes of this rank's SpMMs / event time of the step (SpMM kernel plus "
                              "its split-K reduction launch)"},
     }
+    # DRAM traffic of one SpMM launch: the ncu capture of the kernel (profiles/) shows
+    # dram__bytes_read + dram__bytes_write = 1.024 x the algorithmic bytes (191.98 + 5.37 MB against 192.7 MB);
+    # traffic grows with the bytes streamed, so the average launch of this workload is scaled by that ratio.
+    line["roofline"]["traffic"] = 1.024 * alg_bytes_step / len(order)
+    if world == 1:
+        line["comparators"] = {"cublas_dense_fp16": cublas_dense(dev, acts, order, args)}
     if world == 1 and not args.case:
         line["cpu_baseline"] = cpu_baseline(mats)
         line["encoder"] = encoder_timing(dev)
@@ -309,6 +315,31 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def cublas_dense(dev, acts, order, args):
+    """Dense fp16 GEMM (cuBLAS through torch.mm, fp32 accumulate) on the un-compressed pruned weights, same shapes,
+    same rotation over the matrices; the comparator the reference's drivers use (csrc/spmm_test.cu:101-102)."""
+    dense = [gen_weight(M, K, i, dev) for i, (M, K) in enumerate(SHAPES)]
+    outs = {k: torch.empty((k[1], SHAPES[k[0]][0]), dtype=torch.float16, device=dev) for k in order}
+
+    def step():
+        for k in order:
+            torch.mm(acts[k], dense[k[0]].t(), out=outs[k])
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    dense_bytes = sum(2 * SHAPES[i][0] * SHAPES[i][1] for (i, N) in order)
+    return {"value": flops_per_step() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+            "dense_weight_gbs": dense_bytes / (ms * 1e-3) / 1e9}
 
 
 def cpu_baseline(mats):

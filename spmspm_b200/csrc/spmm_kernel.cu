@@ -3,15 +3,15 @@
 // Replaces the reference's SpMM_Kernel_bitmap_v3 (reference csrc/SpMM_Kernel.cuh:18-199,
 // an mma.sync + cp.async kernel) with a persistent, warp-specialised kernel:
 //
-//   producer warp   streams the compressed weight (packed values, bitmaps, median
-//                   offsets of two vertically adjacent 64x64 global tiles) with
-//                   1-D bulk copies and the activation tile with a 2-D TMA load into a
-//                   ring of shared-memory stages, completion on mbarriers;
-//   decode warps    (groups of 4 warps, one thread per weight row) expand the bitmaps:
-//                   a first pass turns the 128 tile bitmaps of the stage into per-row
-//                   value offsets with byte-wise popcounts + a 16-lane prefix sum, a second
-//                   pass
-//                   gathers each row's values and writes the dense 128 x 64 fp16 tile
+//   producer warps  three warps stream the compressed weight (packed values; bitmaps and median
+//                   offsets; activation tiles) of two vertically adjacent 64x64 global tiles with
+//                   1-D bulk copies and the activation tile with a 2-D TMA load into a ring of
+//                   shared-memory stages of four k-tiles each, completion on mbarriers;
+//   decode warps    (4 groups of 4 warps, one group per k-tile of a stage, one thread per weight
+//                   row) expand the bitmaps in a single pass: each thread reads the bitmaps of
+//                   the 8 tiles its row crosses, keeps a running sum of the tile sizes of its
+//                   median tile, finds its row's values with popcounts, expands them with byte
+//                   permutes driven by two nibble tables and writes the dense 128 x 64 fp16 tile
 //                   straight into tensor memory (tcgen05.st) as the MMA's A operand;
 //   MMA warp        one thread issues tcgen05.mma (M=128, N=16..128, K=16, fp16 in,
 //                   fp32 accumulate in TMEM), A from TMEM, B from the swizzled smem tile;
@@ -47,7 +47,6 @@ constexpr int kKT = SPB_KT;
 constexpr int kDecodeGroups = 4;
 constexpr int kSets = kDecodeGroups / kKT;
 static_assert(kKT * kSets == kDecodeGroups, "kKT must be 1, 2 or 4");
-constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
@@ -62,36 +61,10 @@ static_assert(128 * regs_rounded(kRegsControl) + 128 * regs_rounded(kRegsEpilogu
                       128 * kDecodeGroups * regs_rounded(kRegsDecode) <= 65536 - 2048,
               "register budget (keep slack: a resize that can never be satisfied would block for ever)");
 constexpr int kMaxStages = 24;
-// Per-row metadata of one stage, 8 bytes per (tile, row):
-//   word 0  shared-memory byte address of the row's first packed value
-//   word 1  byte 0: 8 * low nibble of the row mask, byte 1: 8 * high nibble (offsets into the
-//           selector tables), byte 2: 2 * number of values in the row
-// Rows (2p, 2p+1) of all 128 tiles form piece p (16 bytes per tile); the pieces are 2080 bytes
-// apart, which makes both the 16-byte writes of pass 1 and the 8-byte reads of pass 2 free of
-// bank conflicts.
-constexpr int kMetaPieceBytes = 128 * 16 + 32;
-constexpr int kMetaBufBytes = 4 * kMetaPieceBytes;
-constexpr int kMetaBytes = ((kDecodeGroups * kMetaBufBytes + kDecodeGroups * 4 * 32 + 1023) / 1024) * 1024;
 constexpr int kHeaderBytes = 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
-// Optional cycle accounting of the decode warps (debug builds only: -DSPB_TIMING).
-#ifdef SPB_TIMING
-#define SPB_TDECL long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t6 = 0
-#define SPB_T(x) x = clock64()
-#define SPB_ACC(i, v) tacc[i] += (v)
-#else
-#define SPB_TDECL
-#define SPB_T(x)
-#define SPB_ACC(i, v)
-#endif
 
-#ifdef SPB_TIMELINE
-__device__ long long g_tl[96][8];
-#define SPB_TL(stage, col) do { if (blockIdx.x == 0 && lane == 0 && (stage) < 96) g_tl[(stage)][(col)] = clock64(); } while (0)
-#else
-#define SPB_TL(stage, col)
-#endif
 
 struct KernelParams {
     const uint16_t* vals;
@@ -211,17 +184,6 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void tc_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
 __device__ __forceinline__ void tc_wait_st()
 {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -257,18 +219,6 @@ __device__ __forceinline__ bool elect_one()
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
     return pred != 0;
 }
-// AND-reduction of a predicate over the `n` threads of named barrier `id`.
-__device__ __forceinline__ bool bar_and(int id, int n, bool pred)
-{
-    uint32_t out;
-    asm volatile(
-        "{ .reg .pred p, q; setp.ne.u32 p, %3, 0; barrier.cta.red.and.pred q, %1, %2, p; selp.u32 %0, 1, 0, q; }"
-        : "=r"(out)
-        : "r"(id), "r"(n), "r"((uint32_t)pred)
-        : "memory");
-    return out != 0;
-}
-
 // Shared-memory descriptor of a K-major, 128-byte-swizzled tile (rows of 64 fp16 = 128 B,
 // 8-row groups 1024 B apart), as written by the 2-D TMA load of the activation tile.
 __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr)
@@ -316,6 +266,12 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
     uint32_t d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
+}
+__device__ __forceinline__ void tc_st_32x32b_x8(uint32_t taddr, const uint32_t* r)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr)
 {
@@ -371,25 +327,45 @@ __device__ __forceinline__ uint2 lut_high_entry(uint32_t n)
     return make_uint2(pair_sel_top(b6, b7) | (win << 16), pair_sel_top(b4, b5));
 }
 
-// Expansion of one 8-element row segment described by its two metadata words into 4 registers of
-// packed fp16, split into a load half and a compute half so that the loads of several segments can
-// be in flight together.  lut: shared address of the selector tables (a link-time constant).
+// Expansion of one 8-element row segment (one row of one 8x8 tile) into 4 registers of packed fp16,
+// split into a load half and a compute half so that the loads of several segments can be in flight
+// together.  lut: shared address of the selector tables.
 #ifndef SPB_UNIT_BATCH
-#define SPB_UNIT_BATCH 1
+#define SPB_UNIT_BATCH 2
 #endif
 constexpr int kUnitBatch = SPB_UNIT_BATCH;  // row segments whose loads are issued together (1, 2 or 4)
 struct UnitLoads {
     uint32_t x0, x1, x2, y0, y1, y2, l0, l1, h0, h1, sb, st;
 };
-__device__ __forceinline__ void unit_load(uint32_t w0, uint32_t w1, uint32_t lut, UnitLoads& u)
+__device__ __forceinline__ void lds32x3_before(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c)
 {
-    const uint32_t ilo = prmt(w1, 0u, 0x4440u), ihi = prmt(w1, 0u, 0x4441u), k2 = prmt(w1, 0u, 0x4442u);
+    asm volatile("ld.shared.b32 %0, [%3+-8];\n\tld.shared.b32 %1, [%3+-4];\n\tld.shared.b32 %2, [%3];"
+                 : "=&r"(a), "=&r"(b), "=&r"(c)
+                 : "r"(addr));
+}
+// Load half: everything a row segment needs is derived from the tile's 64-bit bitmap (lo, hi)
+// in the thread that expands it.  `run` is the shared address where the values of this tile *pair*
+// (the tile of rows 0-7 and the one of rows 8-15 of the same 16-row median tile and 8-column slice)
+// start; it is advanced past the pair.  The other tile's count comes from the lane 8 away.
+//   below_lo/below_hi  thread constants: bitmap bits of the tile rows above this thread's row
+//   rsel               permute selector moving this row's mask byte to byte 0
+//   second             all ones in the threads of the second tile of the pair, else zero
+__device__ __forceinline__ void unit_load_sp(uint32_t lo, uint32_t hi, uint32_t& run, uint32_t below_lo,
+                                             uint32_t below_hi, uint32_t rsel, uint32_t second, uint32_t lut,
+                                             UnitLoads& u)
+{
+    const uint32_t cnt = __popc(lo) + __popc(hi);
+    const uint32_t other = __shfl_xor_sync(0xffffffffu, cnt, 8);
+    const uint32_t tile = run + 2u * (other & second);
+    run += 2u * (cnt + other);
+    const uint32_t w0 = tile + 2u * (__popc(lo & below_lo) + __popc(hi & below_hi));
+    const uint32_t g = prmt(lo, hi, rsel);                 // row mask in byte 0 (bytes 1-3 are not clean)
+    const uint32_t wt = w0 + 2u * __popc(g & 0xffu);       // address just past the row's last value
     lds32x3(w0 & ~3u, u.x0, u.x1, u.x2);
-    const uint32_t wt = w0 + k2 - 8u;  // address of the value 4 before the row's end
-    lds32x3(wt & ~3u, u.y0, u.y1, u.y2);
-    lds64(lut + ilo, u.l0, u.l1);
-    lds64(lut + 128u + ihi, u.h0, u.h1);
-    u.sb = w0 << 3;  // funnel shifts use the low 5 bits: 0 or 16
+    lds32x3_before(wt & ~3u, u.y0, u.y1, u.y2);            // window of the 4 values before wt
+    lds64(lut + (g & 15u) * 8u, u.l0, u.l1);
+    lds64(lut + 128u + (g & 0xf0u), u.h0, u.h1);           // high-nibble entries are 16 bytes apart
+    u.sb = w0 << 3;
     u.st = wt << 3;
 }
 __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
@@ -406,7 +382,9 @@ template <int NPAD>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtensorMap tmap_b)
 {
-    __shared__ __align__(16) uint2 lut_tab[32];  // selector tables: low nibble [0,16), high nibble [16,32)
+    // selector tables: low nibble entries [0,16); high nibble entry n at index 16 + 2n (16 bytes apart,
+    // so that the nibble's bit position can be used as the offset)
+    __shared__ __align__(16) uint2 lut_tab[48];
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled activation tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -428,7 +406,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t off_mt0 = off_bm1 + kKT * 512, off_mt1 = off_mt0 + kKT * 16;
     const uint32_t off_rel = off_mt1 + kKT * 16;  // [2][kKT] uint32: byte offset of a tile's values in its run
     const uint32_t stage_bytes = (off_rel + 8 * kKT + 1023) & ~1023u;
-    const uint32_t avail = p.smem_bytes - pad - kHeaderBytes - kMetaBytes;
+    const uint32_t avail = p.smem_bytes - pad - kHeaderBytes;
     int S = (int)(avail / stage_bytes);
     if (S > kMaxStages) S = kMaxStages;
 
@@ -440,8 +418,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kSets + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-    uint8_t* meta_base = smem + kHeaderBytes;
-    const uint32_t stage0 = smem_u32(smem + kHeaderBytes + kMetaBytes);
+    const uint32_t stage0 = smem_u32(smem + kHeaderBytes);
 
     // Back-to-back tcgen05.mma into one accumulator are serialised by the tensor core, and at these
     // tiny N every instruction is pure latency, so the four k-steps of a k-tile go to different
@@ -468,7 +445,12 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     }
     if (threadIdx.x >= 32 && threadIdx.x < 64) {
         const uint32_t n = threadIdx.x - 32;
-        lut_tab[n] = n < 16 ? lut_low_entry(n) : lut_high_entry(n - 16);
+        if (n < 16) {
+            lut_tab[n] = lut_low_entry(n);
+        } else {
+            lut_tab[16 + 2 * (n - 16)] = lut_high_entry(n - 16);
+            lut_tab[17 + 2 * (n - 16)] = make_uint2(0u, 0u);
+        }
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
@@ -540,8 +522,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             };
             uint32_t slot = 0, round = 0;
             bool ok = true;
-            SPB_TDECL;
-            int tl_stage = 0;
             int item = blockIdx.x, kk0 = 0;
             Item w = decode_item(p, item < p.num_items ? item : 0);
             if (item < p.num_items && w.nk == 0) item = next_nonempty(item, w);
@@ -575,12 +555,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 const int a1 = __shfl_sync(0xffffffffu, cur.v1, bidx), e1 = __shfl_sync(0xffffffffu, cur.v1, bidx + nv);
                 const int r0 = __shfl_sync(0xffffffffu, cur.v0, bidx + (lane & 7));
                 const int r1 = __shfl_sync(0xffffffffu, cur.v1, bidx + (lane & 7));
-                SPB_T(t0);
                 if (round > 0) ok = mbar_wait_patient(bar_empty + 8 * slot, (round - 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                SPB_T(t1);
-                if (prole == 0) SPB_TL(tl_stage, 0);
                 uint32_t n0 = (uint32_t)(e0 - a0) * 2, n1 = chunk1 ? (uint32_t)(e1 - a1) * 2 : 0u;
                 if (e0 < a0 || n0 > (uint32_t)nv * vmax || (chunk1 && (e1 < a1 || n1 > (uint32_t)nv * vmax))) {
                     if (lane == 0 && prole == 0) atomicOr(p.status, (int)kStatusBadOffsets);
@@ -621,20 +598,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     }
                 }
                 __syncwarp();
-                SPB_TL(tl_stage, 1 + prole);
-                ++tl_stage;
-                SPB_T(t2);
-                SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
                 if (++slot == (uint32_t)S) {
                     slot = 0;
                     ++round;
                 }
             }
-#ifdef SPB_TIMING
-            if (blockIdx.x == 0 && lane == 0)
-                printf("producer: stages=%lld wait_empty=%lld issue=%lld S=%d stage_bytes=%u\n", tacc[6], tacc[0] / tacc[6],
-                       tacc[1] / tacc[6], S, stage_bytes);
-#endif
         } else if (warp == kMmaWarp) {
             // ================================================================= MMA issuer
             // The whole warp runs the loop with warp-uniform state (so addresses and descriptors stay
@@ -646,8 +614,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             uint32_t idx = 0, slot = 0, abuf = 0, apar = 0;
             bool ok = true;
-            int tl_stage = 0;
-            SPB_TDECL;
             for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
                 const Item w = decode_item(p, item);
                 if (w.nk == 0) continue;
@@ -658,11 +624,8 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 const uint32_t d_tmem = tmem_base + accbuf * (kNAcc * NPAD);
                 for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT) {
                     const int nv = min(kKT, w.nk - kk0);
-                    SPB_T(t0);
                     ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_aready + 8 * abuf, apar, abort_flag));
                     if (!ok) break;
-                    SPB_T(t1);
-                    SPB_TL(tl_stage, 6);
                     tc_fence_after();
                     const uint32_t sbase = stage0 + slot * stage_bytes;
                     if (elect_one()) {
@@ -677,10 +640,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         tc_commit(bar_empty + 8 * slot);
                     }
                     __syncwarp();
-                    SPB_TL(tl_stage, 7);
-                    ++tl_stage;
-                    SPB_T(t2);
-                    SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
                     if (++slot == (uint32_t)S) slot = 0;
                     if (++abuf == n_abuf) {
                         abuf = 0;
@@ -691,10 +650,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 __syncwarp();
                 ++idx;
             }
-#ifdef SPB_TIMING
-            if (blockIdx.x == 0 && lane == 0)
-                printf("mma: stages=%lld wait_aready=%lld issue=%lld\n", tacc[6], tacc[0] / tacc[6], tacc[1] / tacc[6]);
-#endif
         }
     } else if (warp < kDecodeWarp0) {
         reg_dealloc<kRegsEpilogue>();
@@ -750,53 +705,42 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     } else {
         // ================================================================= decode
         // Decode group g (4 warps, one per TMEM lane quadrant) belongs to set g / kKT and expands k-tile
-        // g % kKT of every stage of its set.
-        // Every warp works alone: the 32 weight rows of its quadrant cross exactly the 32 bitmap
-        // tiles 32*quad .. 32*quad+31 of the k-tile, so the tile metadata a warp needs in pass 2 is
-        // the metadata its own lanes produce in pass 1.
+        // g % kKT of every stage of its set.  Every warp works alone, one thread per weight row: a row
+        // crosses 8 bitmap tiles per k-tile; the thread reads their bitmaps, keeps a running sum of the
+        // tile sizes inside its 16-row median tile (the other tile of each pair is counted by the lane
+        // 8 away), finds its row's values with popcounts and expands them.
         reg_alloc<kRegsDecode>();
         const int dw = warp - kDecodeWarp0;
         const int group = dw >> 2;
         const int set = group / kKT, sub = group % kKT;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
-        const int row = quad * 32 + lane;      // weight row inside the 128-row block == tile index in pass 1
-        const uint32_t meta = smem_u32(meta_base + group * kMetaBufBytes);
-        uint8_t* cnt_s = meta_base + kDecodeGroups * kMetaBufBytes + dw * 32;  // 32 tile counts of this warp
+        const int row = quad * 32 + lane;      // weight row inside the 128-row block
         const uint32_t lut = smem_u32(lut_tab);
-        // pass 1: this thread owns tile `row` of the k-tile (tile t of global-tile row t>>6)
-        const int chunk = row >> 6, rr = row & 63;
-        const uint32_t p1_addr = meta + (uint32_t)row * 16;
+        const int chunk = row >> 6, rr = row & 63;   // 64-row global-tile row of the block, row inside it
+        const int r_in_tile = rr & 7;
         const uint32_t my_v = chunk ? off_v1 : off_v0;
-        const uint32_t my_bm = (chunk ? off_bm1 : off_bm0) + (uint32_t)sub * 512 + 8 * (uint32_t)rr;
         const uint32_t my_mt = (chunk ? off_mt1 : off_mt0) + (uint32_t)sub * 16 + 4 * (uint32_t)(rr >> 4);
         const uint32_t my_rel = off_rel + 4 * (uint32_t)(chunk * kKT + sub);
-        // byte masks selecting, in the 16 counts of this lane's median tile, the tiles before its own
-        uint32_t before[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int n = (lane & 15) - 4 * i;
-            before[i] = n >= 4 ? 0xffffffffu : (n > 0 ? (1u << (8 * n)) - 1u : 0u);
-        }
-        // pass 2: the 8 tiles crossing this weight row are tbase + 2q, q = 0..7
-        const int tbase = chunk * 64 + 16 * (rr >> 4) + ((rr >> 3) & 1);
-        const int r_in_tile = rr & 7;
-        const uint32_t maddr = meta + (uint32_t)(r_in_tile >> 1) * kMetaPieceBytes + (uint32_t)tbase * 16 +
-                               (uint32_t)(r_in_tile & 1) * 8;
+        // bitmap of the first of the row's 8 tiles (they are 16 bytes apart): median tile rr >> 4, row half
+        // (rr >> 3) & 1 of the 2 x 2 tile order
+        const uint32_t sp_bm = (chunk ? off_bm1 : off_bm0) + (uint32_t)sub * 512 +
+                               8 * (uint32_t)(16 * (rr >> 4) + ((rr >> 3) & 1));
+        const uint32_t below_lo = r_in_tile < 4 ? (1u << (8 * r_in_tile)) - 1u : 0xffffffffu;
+        const uint32_t below_hi = r_in_tile <= 4 ? 0u : (1u << (8 * (r_in_tile - 4))) - 1u;
+        const uint32_t rsel = 0x4440u | (uint32_t)r_in_tile;
+        const uint32_t second = ((rr >> 3) & 1) ? 0xffffffffu : 0u;
 
         uint32_t slot = 0, round = 0, mine = 0;
-        int tl_stage = 0;
         int turn = 0;      // stage counter modulo kSets: this warp's set works when turn == set
         uint32_t abuf = (uint32_t)set;  // TMEM A buffer (in stages) of this set's next stage
         uint32_t bar_old = 0, par_old = 0, bar_new = 0, par_new = 0;  // empty barriers of this set's last two stages
         bool ok = true;
-        SPB_TDECL;
         for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
             const Item w = decode_item(p, item);
             const bool chunk1 = (2 * w.y + 1) < p.gm_total;
             const bool valid = (chunk == 0) || chunk1;
             for (int kk0 = 0; kk0 < w.nk; kk0 += kKT) {
                 if (turn != set) {  // another set's stage: only follow the ring
-                    ++tl_stage;
                     if (++turn == kSets) turn = 0;
                     if (++slot == (uint32_t)S) {
                         slot = 0;
@@ -805,97 +749,16 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     continue;
                 }
                 const bool active = sub < w.nk - kk0;  // this group's k-tile exists in the stage
-                SPB_T(t0);
                 ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                SPB_T(t1);
-                if (sub == 0 && quad == 0) SPB_TL(tl_stage, 4);
                 const uint32_t st = stage0 + slot * stage_bytes;
                 uint32_t a[32];
                 if (active) {
-#if defined(SPB_EXP_NO_DECODE)
-#pragma unroll
-                    for (int q = 0; q < 32; ++q) a[q] = 0;
-                    uint32_t m0[8], m1[8];
-#else
-                    // ---- pass 1: per-row value addresses, table offsets and counts of tile `row`
-                    {
-                        uint32_t bmx = 0, bmy = 0, mt = 0, rel = 0;
-                        if (valid) {
-                            lds64(st + my_bm, bmx, bmy);
-                            mt = lds32(st + my_mt);
-                            rel = lds32(st + my_rel);
-                        }
-                        // per-byte population counts (one byte of the bitmap = one tile row)
-                        uint32_t ca = bmx - ((bmx >> 1) & 0x55555555u);
-                        ca = (ca & 0x33333333u) + ((ca >> 2) & 0x33333333u);
-                        ca = (ca + (ca >> 4)) & 0x0f0f0f0fu;
-                        uint32_t cb = bmy - ((bmy >> 1) & 0x55555555u);
-                        cb = (cb & 0x33333333u) + ((cb >> 2) & 0x33333333u);
-                        cb = (cb + (cb >> 4)) & 0x0f0f0f0fu;
-                        const uint32_t ia = ca * 0x01010101u, ib = cb * 0x01010101u;  // inclusive byte prefixes
-                        const uint32_t tl = ia >> 24;
-                        cnt_s[lane] = (uint8_t)(tl + (ib >> 24));
-                        __syncwarp();
-                        // values of the tiles that precede this one inside its 16-tile median tile
-                        uint32_t c0, c1, c2, c3;
-                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                                     : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
-                                     : "r"(smem_u32(cnt_s) + (lane & 16)));
-                        c0 &= before[0];
-                        c1 &= before[1];
-                        c2 &= before[2];
-                        c3 &= before[3];
-                        const uint32_t h = (c0 & 0x00ff00ffu) + ((c0 >> 8) & 0x00ff00ffu) + (c1 & 0x00ff00ffu) +
-                                           ((c1 >> 8) & 0x00ff00ffu) + (c2 & 0x00ff00ffu) + ((c2 >> 8) & 0x00ff00ffu) +
-                                           (c3 & 0x00ff00ffu) + ((c3 >> 8) & 0x00ff00ffu);
-                        const uint32_t excl = (h & 0xffffu) + (h >> 16);
-                        // byte offset of the tile's first value in its run; clamped so that corrupt
-                        // median offsets can never point outside the stage (the bitmaps follow the values)
-                        const uint32_t in_run = min(rel + 2 * (mt + excl), (uint32_t)kKT * vmax);
-                        const uint32_t abs_lo = st + my_v + in_run;  // address of the tile's first value
-                        const uint32_t abs_hi = abs_lo + 2 * tl;
-                        const uint32_t ea = ia << 8, eb = ib << 8;    // exclusive row prefixes, byte 0 == 0
-                        const uint32_t il_lo = (bmx & 0x0f0f0f0fu) << 3, ih_lo = (bmx >> 1) & 0x78787878u, k_lo = ca << 1;
-                        const uint32_t il_hi = (bmy & 0x0f0f0f0fu) << 3, ih_hi = (bmy >> 1) & 0x78787878u, k_hi = cb << 1;
-                        uint32_t w0[8], w1[8];
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) {
-                            const uint32_t s1 = (uint32_t)r | ((uint32_t)(4 + r) << 4);
-                            const uint32_t s2 = 0x0010u | ((uint32_t)(4 + r) << 8) | ((uint32_t)(4 + r) << 12);
-                            w0[r] = prmt(ea, 0u, 0x4440u | (uint32_t)r) * 2u + abs_lo;
-                            w0[4 + r] = prmt(eb, 0u, 0x4440u | (uint32_t)r) * 2u + abs_hi;
-                            w1[r] = prmt(prmt(il_lo, ih_lo, s1), k_lo, s2);
-                            w1[4 + r] = prmt(prmt(il_hi, ih_hi, s1), k_hi, s2);
-                        }
-#pragma unroll
-                        for (int pc = 0; pc < 4; ++pc)
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p1_addr + pc * kMetaPieceBytes),
-                                         "r"(w0[2 * pc]), "r"(w1[2 * pc]), "r"(w0[2 * pc + 1]), "r"(w1[2 * pc + 1])
-                                         : "memory");
-                    }
-                    __syncwarp();
-                    // ---- pass 2, first half: thread <-> weight row; gather its values, 8 per tile
-                    uint32_t m0[8], m1[8];
-#if defined(SPB_EXP_NO_PASS2)
-#pragma unroll
-                    for (int q = 0; q < 32; ++q) a[q] = 0;
-#else
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) lds64(maddr + 32 * q, m0[q], m1[q]);
-#pragma unroll
-                    for (int q0 = 0; q0 < 4; q0 += kUnitBatch) {
-                        UnitLoads u[kUnitBatch];
-#pragma unroll
-                        for (int q = 0; q < kUnitBatch; ++q) unit_load(m0[q0 + q], m1[q0 + q], lut, u[q]);
-#pragma unroll
-                        for (int q = 0; q < kUnitBatch; ++q) unit_expand(u[q], a + 4 * (q0 + q));
-                    }
-#endif
-#endif
-                    // the TMEM A buffer may be rewritten once the MMAs that read it have completed
-                    bool fr = true;
+                    // ---- thread <-> weight row.  Per batch of row segments: the bitmaps of their tiles, each
+                    // tile's start (running sum over the median tile), the row's start, the expansion, and
+                    // the store of the finished registers to tensor memory.
+                    bool fr = true;  // the TMEM A buffer may be rewritten once the MMAs that read it have completed
                     if (reuse_wait) {
                         if (two_deep) {
                             if (mine >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
@@ -905,23 +768,38 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     }
                     fr = __all_sync(0xffffffffu, fr);
                     const uint32_t ta = tmem_a0 + (abuf * kKT + (uint32_t)sub) * 32 + ((uint32_t)(quad * 32) << 16);
-                    if (fr) {
-                        tc_fence_after();
-                        tc_st_32x32b_x16(ta, a);
+                    if (fr) tc_fence_after();
+                    uint32_t run = st + my_v;
+                    if (valid) {
+                        const uint32_t mt = lds32(st + my_mt), rel = lds32(st + my_rel);
+                        // clamped so that corrupt offsets can never point outside the stage
+                        run += min(rel + 2 * mt, (uint32_t)kKT * vmax);
                     }
-                    // ---- pass 2, second half
-#if !defined(SPB_EXP_NO_PASS2) && !defined(SPB_EXP_NO_DECODE)
 #pragma unroll
-                    for (int q0 = 4; q0 < 8; q0 += kUnitBatch) {
+                    for (int q0 = 0; q0 < 8; q0 += kUnitBatch) {
+                        uint32_t blo[kUnitBatch], bhi[kUnitBatch];
                         UnitLoads u[kUnitBatch];
 #pragma unroll
-                        for (int q = 0; q < kUnitBatch; ++q) unit_load(m0[q0 + q], m1[q0 + q], lut, u[q]);
+                        for (int q = 0; q < kUnitBatch; ++q) {
+                            blo[q] = bhi[q] = 0u;
+                            if (valid) lds64(st + sp_bm + 16 * (q0 + q), blo[q], bhi[q]);
+                        }
+#pragma unroll
+                        for (int q = 0; q < kUnitBatch; ++q)
+                            unit_load_sp(blo[q], bhi[q], run, below_lo, below_hi, rsel, second, lut, u[q]);
 #pragma unroll
                         for (int q = 0; q < kUnitBatch; ++q) unit_expand(u[q], a + 4 * (q0 + q));
+                        if (fr) {
+                            if (kUnitBatch == 4) {
+                                tc_st_32x32b_x16(ta + 4 * q0, a + 4 * q0);
+                            } else if (kUnitBatch == 2) {
+                                tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
+                            } else if (q0 & 1) {
+                                tc_st_32x32b_x8(ta + 4 * (q0 - 1), a + 4 * (q0 - 1));
+                            }
+                        }
                     }
-#endif
                     if (fr) {
-                        tc_st_32x32b_x16(ta + 16, a + 16);
                         tc_wait_st();
                         tc_fence_before();
                     }
@@ -945,8 +823,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     mbar_arrive(bar_aready + 8 * abuf);
                     mbar_arrive(bar_empty + 8 * slot);
                 }
-                if (sub == 0 && quad == 0) SPB_TL(tl_stage, 5);
-                ++tl_stage;
                 bar_old = bar_new;
                 par_old = par_new;
                 bar_new = bar_empty + 8 * slot;
@@ -959,15 +835,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     slot = 0;
                     ++round;
                 }
-                SPB_T(t2);
-                SPB_ACC(0, t1 - t0); SPB_ACC(1, t2 - t1); SPB_ACC(6, 1);
                 if (!ok) break;
             }
         }
-#ifdef SPB_TIMING
-        if (blockIdx.x == 0 && lane == 0 && (dw % 5) == 0)
-            printf("decode warp %d: stages=%lld wait_full=%lld work=%lld\n", dw, tacc[6], tacc[0] / tacc[6], tacc[1] / tacc[6]);
-#endif
     }
 
     // ---- teardown ----------------------------------------------------------------------------
@@ -985,15 +855,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
         __syncthreads();
     }
-#ifdef SPB_TIMELINE
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        const long long t00 = g_tl[0][0];
-        printf("stage: prod_go p0_done p1_done p2_done | dec_got dec_done | mma_go mma_done  (clk, S=%d)\n", S);
-        for (int i = 0; i < 40; ++i)
-            printf("%3d: %7lld %7lld %7lld %7lld | %7lld %7lld | %7lld %7lld\n", i, g_tl[i][0] - t00, g_tl[i][1] - t00,
-                   g_tl[i][2] - t00, g_tl[i][3] - t00, g_tl[i][4] - t00, g_tl[i][5] - t00, g_tl[i][6] - t00, g_tl[i][7] - t00);
-    }
-#endif
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
