@@ -161,6 +161,8 @@ def main():
     ap.add_argument("--case", default=None,
                     help="M,K,N[,sparsity[,split_k]]: time one SpMM shape instead of the OPT-13B set "
                          "(used for per-shape tables and for small profiler captures)")
+    ap.add_argument("--schedule", default="auto", choices=["auto", "static", "balanced"],
+                    help="work schedule of the SpMM kernel (spb_set_schedule); auto lets the library choose per call")
     args = ap.parse_args()
     global SHAPES, NS, SPARSITY, WORKLOAD
     forced_split = None
@@ -184,6 +186,7 @@ def main():
 
     import torch.distributed as dist
     import spmspm_b200 as sp
+    sp.set_schedule({"auto": sp.SCHEDULE_AUTO, "static": sp.SCHEDULE_STATIC, "balanced": sp.SCHEDULE_BALANCED}[args.schedule])
     from spmspm_b200 import dist as spd
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
@@ -288,6 +291,7 @@ def main():
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "shapes": SHAPES, "N": NS, "sparsity": SPARSITY, "spmm_per_step": len(order),
                    "split_k": {f"{SHAPES[i][0]}x{SHAPES[i][1]}xN{N}": splits[(i, N)] for (i, N) in order},
+                   "schedule": args.schedule,
                    "parallelism": f"tp{world}_m_split_allgather" if world > 1 else "single_gpu",
                    "l2": f"inputs larger than L2: {weight_bytes / 1e6:.0f} MB of compressed weights per rank "
                          "rotate between reuses"},

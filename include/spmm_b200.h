@@ -146,6 +146,26 @@ int spb_splitk_reduce(void* stream, uint16_t* C, const uint16_t* Reduction_Works
 int spb_suggest_split_k(int M, int N, int K);
 
 /*
+ * Work schedule of spb_spmm_bitmap_v3 (no counterpart in the reference, whose grid is one CTA per
+ * output tile and split-K range, csrc/SpMM_API.cuh:61-67).
+ *   SPB_SCHEDULE_STATIC: one work item per 128-row block and split-K range, no scratch.
+ *   SPB_SCHEDULE_BALANCED: the k-tiles of all ranges are laid end to end and every SM takes an equal
+ *     share; a range that is cut between SMs is summed in fp32 through scratch memory the library owns
+ *     (about 14 MB per stream, created on a stream's first call), and rounded to fp16 once, where the
+ *     reference rounds it.  The scratch belongs to the stream: a call captured into a CUDA graph uses
+ *     the scratch an earlier, uncaptured call on the capturing stream created (the static schedule if
+ *     there was none), so such a graph must not run at the same time as other calls made on that
+ *     stream.  Calls on more than 8 streams and spb_spmm_bitmap_v3_noalloc use the static schedule.
+ *   SPB_SCHEDULE_AUTO (default): per call, whichever of the two a cost model expects to be faster.
+ * Both give the same result up to the order of the fp32 additions inside a range.
+ * Returns the previous mode, or -1 for an invalid mode.  Process-wide.
+ */
+#define SPB_SCHEDULE_AUTO 0
+#define SPB_SCHEDULE_STATIC 1
+#define SPB_SCHEDULE_BALANCED 2
+int spb_set_schedule(int mode);
+
+/*
  * Status word of the current device: 0 when no kernel of this library has hit a
  * bounded wait that ran out or an inconsistent offset since the last reset.
  * Synchronises the device.  spb_reset_device_status clears it.

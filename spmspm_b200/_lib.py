@@ -32,6 +32,7 @@ SIGNATURES = {
                                                   ctypes.c_int, ctypes.c_int]),
     "spb_splitk_reduce": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "spb_suggest_split_k": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
+    "spb_set_schedule": (ctypes.c_int, [ctypes.c_int]),
     "spb_device_status": (ctypes.c_int, [_i32p]),
     "spb_reset_device_status": (ctypes.c_int, []),
 }

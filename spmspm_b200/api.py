@@ -205,6 +205,17 @@ def suggest_split_k(M, N, K):
     return _lib.load().spb_suggest_split_k(M, N, K)
 
 
+SCHEDULE_AUTO, SCHEDULE_STATIC, SCHEDULE_BALANCED = 0, 1, 2
+
+
+def set_schedule(mode):
+    """spb_set_schedule: SCHEDULE_AUTO (default), SCHEDULE_STATIC or SCHEDULE_BALANCED; returns the previous mode."""
+    prev = _lib.load().spb_set_schedule(int(mode))
+    if prev < 0:
+        raise SpmmError("set_schedule: mode must be SCHEDULE_AUTO, SCHEDULE_STATIC or SCHEDULE_BALANCED")
+    return prev
+
+
 def spmm(W: BitmapMatrix, B, split_k=None, out=None, workspace=None, stream=None):
     """C[N,M] = (W @ B^T)^T with B given as [N,K] (the reference's column-major K x N)."""
     if not (B.is_cuda and B.dtype == torch.float16 and B.dim() == 2 and B.is_contiguous() and B.shape[1] == W.K):

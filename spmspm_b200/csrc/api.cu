@@ -312,6 +312,13 @@ int spb_splitk_reduce(void* stream, uint16_t* C, const uint16_t* Reduction_Works
 
 int spb_suggest_split_k(int M, int N, int K) { return spb::suggest_split_k(M, N, K); }
 
+int spb_set_schedule(int mode)
+{
+    const int prev = spb::set_schedule(mode);
+    if (prev < 0) spb::set_error("spb_set_schedule: mode must be SPB_SCHEDULE_AUTO, SPB_SCHEDULE_STATIC or SPB_SCHEDULE_BALANCED");
+    return prev;
+}
+
 int spb_device_status(int* status_out)
 {
     int* p = nullptr;
@@ -326,6 +333,11 @@ int spb_reset_device_status(void)
 {
     int* p = nullptr;
     cudaError_t e = spb::device_status_ptr(&p);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    // a kernel that gave up may have left arrival counters of the balanced schedule behind
+    e = spb::reset_schedule_scratch();
     if (e != cudaSuccess) return (int)e;
     return (int)cudaMemset(p, 0, sizeof(int));
 }

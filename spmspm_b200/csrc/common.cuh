@@ -42,6 +42,13 @@ struct SpmmArgs {
 };
 cudaError_t spmm_launch(cudaStream_t s, const SpmmArgs& a);
 int suggest_split_k(int M, int N, int K);
+// Work schedule of the SpMM kernel: 1 = static (one work item per split-K range, no scratch), 2 = balanced
+// (equal k-tile shares per SM, fp32 exchange through library-owned scratch) whenever possible, 0 = whichever
+// the cost model expects to be faster for the shape.
+int set_schedule(int mode);          // returns the previous mode, -1 for an invalid one
+void push_static_schedule();         // calling thread only, nestable
+void pop_static_schedule();
+cudaError_t reset_schedule_scratch();  // clears the arrival counters of the current device
 
 void set_error(const char* fmt, ...);
 

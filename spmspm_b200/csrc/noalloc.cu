@@ -63,6 +63,10 @@ extern "C" int spb_spmm_bitmap_v3_noalloc(void* stream, const uint16_t* Compress
     }
     // The SpMM kernel writes every partial of every range (empty ranges as zeros) before the reduction
     // reads them, so nothing in the scratch has to be cleared between calls.
-    return spb_spmm_bitmap_v3(stream, nullptr, Compressed_A, TileOffsets, TileOffsets_Median, bitmap, max_nnz_intile, B,
-                              C, M_Global, N_Global, K_Global, ws, Split_K);
+    // The static work schedule is the one that needs no library-owned buffers.
+    spb::push_static_schedule();
+    const int rc = spb_spmm_bitmap_v3(stream, nullptr, Compressed_A, TileOffsets, TileOffsets_Median, bitmap,
+                                      max_nnz_intile, B, C, M_Global, N_Global, K_Global, ws, Split_K);
+    spb::pop_static_schedule();
+    return rc;
 }

@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cstdio>
+#include <atomic>
 #include <mutex>
 
 namespace spb {
@@ -51,15 +52,17 @@ constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
 constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kDecodeGroups);
-// Registers per thread after the roles have resized (the launch gives every thread
-// 65536 / kThreads rounded down to a multiple of 8).
+// Registers per thread after the roles have resized.  A CTA owns the registers it was launched with,
+// kRegsLaunch per thread (65536 / kThreads rounded down to a multiple of 8, what ptxas reports for the
+// kernel), and a warp that grows can only take what other warps of the CTA have given back: if the sizes
+// below added up to more than the launch allocation, the last warps to grow would block for ever.
+constexpr int kRegsLaunch = 65536 / kThreads / 8 * 8;
 constexpr int kRegsControl = 40, kRegsEpilogue = 56, kRegsDecode = 96;
-// The register file is handed out per warp in blocks of 512 registers (16 per thread), so the budget
-// is checked on rounded-up sizes; a resize that cannot be satisfied blocks the warp for ever.
-constexpr int regs_rounded(int r) { return (r + 15) / 16 * 16; }
-static_assert(128 * regs_rounded(kRegsControl) + 128 * regs_rounded(kRegsEpilogue) +
-                      128 * kDecodeGroups * regs_rounded(kRegsDecode) <= 65536 - 2048,
-              "register budget (keep slack: a resize that can never be satisfied would block for ever)");
+static_assert(kRegsControl % 8 == 0 && kRegsEpilogue % 8 == 0 && kRegsDecode % 8 == 0, "register counts come in eights");
+static_assert(128 * kRegsControl + 128 * kRegsEpilogue + 128 * kDecodeGroups * kRegsDecode <= kRegsLaunch * kThreads,
+              "register budget: the resized roles must fit into the CTA's launch allocation");
+static_assert(kRegsControl <= kRegsLaunch && kRegsEpilogue <= kRegsLaunch && kRegsDecode >= kRegsLaunch,
+              "roles that shrink must not exceed, roles that grow must not undercut the launch allocation");
 constexpr int kMaxStages = 24;
 constexpr int kHeaderBytes = 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -77,6 +80,10 @@ struct KernelParams {
     int M, N, K, split_k;
     int kt_total, avg_kt, row_blocks, gm_total, n_tiles, num_items;
     uint32_t smem_bytes;
+    // balanced schedule: fp32 sums of partial runs, 2 slots of 128 x NPAD per CTA, and one arrival counter per item
+    float* partials;
+    int* counters;
+    int balanced, units;
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -232,23 +239,146 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr)
     return d;
 }
 
+// Named barrier 1: the 128 threads of the epilogue warps.
+__device__ __forceinline__ void bar_sync_epilogue()
+{
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+__device__ __forceinline__ bool bar_and_epilogue(bool pred)
+{
+    uint32_t r;
+    asm volatile(
+        "{ .reg .pred p, q; setp.ne.u32 p, %1, 0; bar.red.and.pred q, 1, 128, p; selp.u32 %0, 1, 0, q; }"
+        : "=r"(r)
+        : "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
+// A work item is a run of k-tiles of one 128-row block (and one activation tile column): a whole split-K
+// range, or, with the balanced schedule, a piece of one.
+__device__ __forceinline__ int ld_acquire_gpu(const int* p)
+{
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 struct Item {
     int nt, y, batch, k0, nk;
+    int id;        // index of the (activation tile, row block, split-K range) this run belongs to
+    bool partial;  // the run does not cover its whole range: its sum goes through the fp32 scratch
 };
-__device__ __forceinline__ Item decode_item(const KernelParams& p, int item)
+// Start of CTA c's share of the units (k-tiles of all row blocks, in item order) under the balanced schedule.
+// The host only chooses this schedule when (units + 1) * gridDim.x fits into 31 bits.
+__device__ __forceinline__ int share_begin(const KernelParams& p, int c)
 {
-    Item it;
-    const int per_nt = p.row_blocks * p.split_k;
-    it.nt = item / per_nt;
-    const int rem = item - it.nt * per_nt;
-    it.y = rem / p.split_k;
-    it.batch = rem - it.y * p.split_k;
-    it.k0 = it.batch * p.avg_kt;
-    int k1 = it.k0 + p.avg_kt;
-    if (k1 > p.kt_total) k1 = p.kt_total;
-    it.nk = k1 > it.k0 ? k1 - it.k0 : 0;
-    return it;
+    return (int)(((uint32_t)c * (uint32_t)p.units) / gridDim.x);
 }
+// The CTA whose share holds unit u: the largest c with share_begin(c) <= u.
+__device__ __forceinline__ int share_owner(const KernelParams& p, int u)
+{
+    return (int)((((uint32_t)u + 1u) * gridDim.x - 1u) / (uint32_t)p.units);
+}
+// Walks the work items of this CTA.  Static schedule: items blockIdx.x, + gridDim.x, ... with the
+// split-K ranges cut exactly like the reference's (reference csrc/SpMM_Kernel.cuh:35-43).  Balanced
+// schedule: all k-tiles of all ranges are laid end to end and every CTA takes an equal share of them; a
+// share is cut into runs at the range boundaries.  The runs that cover only part of their range (at most
+// the first and the last of the share) come first, the shorter one before the longer one, then the
+// whole ranges: the exchange of partial sums then happens while the CTA still has work, and the last
+// run of a CTA is long enough to hide it.
+struct Walk {
+    int begin, end;      // this CTA's share (balanced) / next item and item count (static)
+    int lo_end, hi_beg;  // end of the partial run at the low end, start of the one at the high end
+    int pos, phase;      // position inside the current phase (-1: not entered), phase 0..2
+    int order;           // which part each phase walks: 2 bits per phase, 0 low run, 1 high run, 2 middle, 3 nothing
+    __device__ __forceinline__ void range_of(const KernelParams& p, int u, int& r0, int& r1) const
+    {
+        const int row = u / p.kt_total, k = u - row * p.kt_total;
+        const int ks = (k / p.avg_kt) * p.avg_kt;
+        int ke = ks + p.avg_kt;
+        if (ke > p.kt_total) ke = p.kt_total;
+        r0 = row * p.kt_total + ks;
+        r1 = row * p.kt_total + ke;
+    }
+    __device__ __forceinline__ void init(const KernelParams& p)
+    {
+        pos = -1;
+        phase = 0;
+        if (!p.balanced) {
+            begin = blockIdx.x;
+            end = p.num_items;
+            lo_end = hi_beg = order = 0;
+            return;
+        }
+        begin = share_begin(p, blockIdx.x);
+        end = share_begin(p, blockIdx.x + 1);
+        lo_end = begin;
+        hi_beg = end;
+        order = 0x3e;  // middle, nothing, nothing
+        if (begin >= end) return;
+        int r0, r1;
+        range_of(p, begin, r0, r1);
+        const bool lo = r0 != begin || r1 > end;  // the first range of the share is not whole
+        if (lo) lo_end = r1 < end ? r1 : end;
+        bool hi = false;
+        if (lo_end < end) {
+            range_of(p, end - 1, r0, r1);
+            hi = r1 > end;
+            if (hi) hi_beg = r0;  // >= lo_end: both are range boundaries
+        }
+        if (lo && hi)
+            order = (lo_end - begin <= end - hi_beg) ? (0 | 1 << 2 | 2 << 4) : (1 | 0 << 2 | 2 << 4);
+        else if (lo)
+            order = 0 | 2 << 2 | 3 << 4;
+        else if (hi)
+            order = 1 | 2 << 2 | 3 << 4;
+    }
+    __device__ __forceinline__ bool next(const KernelParams& p, Item& it)
+    {
+        if (!p.balanced) {
+            if (begin >= end) return false;
+            const int per_nt = p.row_blocks * p.split_k;
+            it.nt = begin / per_nt;
+            const int rem = begin - it.nt * per_nt;
+            it.y = rem / p.split_k;
+            it.batch = rem - it.y * p.split_k;
+            it.k0 = it.batch * p.avg_kt;  // reference csrc/SpMM_Kernel.cuh:36-43
+            int k1 = it.k0 + p.avg_kt;
+            if (k1 > p.kt_total) k1 = p.kt_total;
+            it.nk = k1 > it.k0 ? k1 - it.k0 : 0;
+            it.id = begin;
+            it.partial = false;
+            begin += gridDim.x;
+            return true;
+        }
+        for (;;) {
+            if (phase > 2) return false;
+            const int part = (order >> (2 * phase)) & 3;
+            const int a = part == 0 ? begin : part == 1 ? hi_beg : lo_end;
+            const int b = part == 0 ? lo_end : part == 1 ? end : part == 2 ? hi_beg : a;
+            if (pos < 0) pos = a;
+            if (pos >= b) {
+                ++phase;
+                pos = -1;
+                continue;
+            }
+            const int row = pos / p.kt_total, k = pos - row * p.kt_total;
+            it.nt = row / p.row_blocks;
+            it.y = row - it.nt * p.row_blocks;
+            it.batch = k / p.avg_kt;
+            const int ks = it.batch * p.avg_kt;
+            int ke = ks + p.avg_kt;
+            if (ke > p.kt_total) ke = p.kt_total;
+            int e = k + (b - pos);
+            if (e > ke) e = ke;
+            it.k0 = k;
+            it.nk = e - k;
+            it.id = row * p.split_k + it.batch;
+            it.partial = k != ks || e != ke;
+            pos += it.nk;
+            return true;
+        }
+    }
+};
 
 __device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t* r)
 {
@@ -392,24 +522,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // ---- carve-up ------------------------------------------------------------------------
-    // A stage holds kKT consecutive k-tiles of one 128-row block: the activation tiles, then for each
-    // of the two 64-row global-tile rows one contiguous run of packed values, the bitmaps and the
-    // median offsets, then the start of every global tile's values inside its run.
-    int max_nnz = *p.max_nnz;
-    if (max_nnz < 8) max_nnz = 8;
-    if (max_nnz > 4096) max_nnz = 4096;
-    const uint32_t vmax = ((uint32_t)max_nnz * 2 + 127) & ~127u;  // bytes per global tile, upper bound
-    constexpr uint32_t kBTile = NPAD * 128;
-    const uint32_t off_v0 = kKT * kBTile, off_v1 = off_v0 + kKT * vmax;
-    const uint32_t off_bm0 = off_v1 + kKT * vmax, off_bm1 = off_bm0 + kKT * 512;
-    const uint32_t off_mt0 = off_bm1 + kKT * 512, off_mt1 = off_mt0 + kKT * 16;
-    const uint32_t off_rel = off_mt1 + kKT * 16;  // [2][kKT] uint32: byte offset of a tile's values in its run
-    const uint32_t stage_bytes = (off_rel + 8 * kKT + 1023) & ~1023u;
-    const uint32_t avail = p.smem_bytes - pad - kHeaderBytes;
-    int S = (int)(avail / stage_bytes);
-    if (S > kMaxStages) S = kMaxStages;
-
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t bar_full = smem_u32(bars);                         // [kMaxStages]
     const uint32_t bar_empty = bar_full + 8 * kMaxStages;             // [kMaxStages]
@@ -418,6 +530,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kSets + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    volatile int* finisher = reinterpret_cast<volatile int*>(tmem_holder + 2);
     const uint32_t stage0 = smem_u32(smem + kHeaderBytes);
 
     // Back-to-back tcgen05.mma into one accumulator are serialised by the tensor core, and at these
@@ -464,6 +577,32 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t tmem_base = *tmem_holder;
     const uint32_t tmem_a0 = tmem_base + kAccCols;
 
+    // Everything above touches only this CTA's shared and tensor memory, so under programmatic dependent
+    // launch it overlaps the tail of the preceding kernel of the stream.  From here on global memory is
+    // read and written: wait until that kernel has completed and its writes are visible.  Kernels queued
+    // behind this one may be set up as soon as every CTA has passed this point.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // ---- carve-up ------------------------------------------------------------------------
+    // A stage holds kKT consecutive k-tiles of one 128-row block: the activation tiles, then for each
+    // of the two 64-row global-tile rows one contiguous run of packed values, the bitmaps and the
+    // median offsets, then the start of every global tile's values inside its run.
+    int max_nnz = *p.max_nnz;
+    if (max_nnz < 8) max_nnz = 8;
+    if (max_nnz > 4096) max_nnz = 4096;
+    const uint32_t vmax = ((uint32_t)max_nnz * 2 + 127) & ~127u;  // bytes per global tile, upper bound
+    constexpr uint32_t kBTile = NPAD * 128;
+    const uint32_t off_v0 = kKT * kBTile, off_v1 = off_v0 + kKT * vmax;
+    const uint32_t off_bm0 = off_v1 + kKT * vmax, off_bm1 = off_bm0 + kKT * 512;
+    const uint32_t off_mt0 = off_bm1 + kKT * 512, off_mt1 = off_mt0 + kKT * 16;
+    const uint32_t off_rel = off_mt1 + kKT * 16;  // [2][kKT] uint32: byte offset of a tile's values in its run
+    const uint32_t stage_bytes = (off_rel + 8 * kKT + 1023) & ~1023u;
+    const uint32_t avail = p.smem_bytes - pad - kHeaderBytes;
+    int S = (int)(avail / stage_bytes);
+    if (S > kMaxStages) S = kMaxStages;
+
+
     // The A operands of n_abuf stages live in TMEM: two per set when the ring is deep enough, else one.
     // A decode warp may overwrite a buffer once the MMAs of the stage n_abuf back have completed, which
     // it learns from that stage's empty barrier; with a ring no deeper than n_abuf the full barrier of
@@ -489,53 +628,60 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             // k-tile base + l of both 64-row global-tile rows) and one batch ahead, so that the latency of
             // these loads never sits between two stages.
             constexpr int kOffBatch = 28;  // k-tiles a batch advances by; a stage needs up to base + 27 + kKT
-            struct Batch {
-                int item, base, v0, v1;
+            // position in the CTA's sequence of non-empty work items
+            struct Cursor {
+                Walk wk;
                 Item w;
+                int seq;
+                bool valid;
+            };
+            auto advance = [&](Cursor& c) {
+                do {
+                    c.valid = c.wk.next(p, c.w);
+                } while (c.valid && c.w.nk == 0);
+                ++c.seq;
+            };
+            struct Batch {
+                Cursor c;
+                int base, v0, v1;
             };
             auto load_batch = [&](Batch& b) {
                 b.v0 = 0;
                 b.v1 = 0;
-                if (prole != 0 || b.item >= p.num_items) return;
-                const size_t g = (size_t)(2 * b.w.y) * p.kt_total + b.w.k0 + b.base;
-                if (lane <= b.w.nk - b.base) {
+                if (prole != 0 || !b.c.valid) return;
+                const size_t g = (size_t)(2 * b.c.w.y) * p.kt_total + b.c.w.k0 + b.base;
+                if (lane <= b.c.w.nk - b.base) {
                     b.v0 = __ldg(p.gtile + g + lane);
-                    if ((2 * b.w.y + 1) < p.gm_total) b.v1 = __ldg(p.gtile + g + p.kt_total + lane);
+                    if ((2 * b.c.w.y + 1) < p.gm_total) b.v1 = __ldg(p.gtile + g + p.kt_total + lane);
                 }
-            };
-            auto next_nonempty = [&](int it, Item& w) -> int {
-                do {
-                    it += gridDim.x;
-                    if (it < p.num_items) w = decode_item(p, it);
-                } while (it < p.num_items && w.nk == 0);
-                return it;
             };
             auto batch_after = [&](const Batch& b) -> Batch {
                 Batch n = b;
-                if (b.base + kOffBatch < b.w.nk) {
+                if (b.base + kOffBatch < b.c.w.nk) {
                     n.base = b.base + kOffBatch;
                 } else {
                     n.base = 0;
-                    n.item = next_nonempty(b.item, n.w);
+                    if (n.c.valid) advance(n.c);
                 }
                 return n;
             };
             uint32_t slot = 0, round = 0;
             bool ok = true;
-            int item = blockIdx.x, kk0 = 0;
-            Item w = decode_item(p, item < p.num_items ? item : 0);
-            if (item < p.num_items && w.nk == 0) item = next_nonempty(item, w);
+            int kk0 = 0;
+            Cursor st;
+            st.wk.init(p);
+            st.seq = -1;
+            advance(st);
             Batch cur;
-            cur.item = item;
+            cur.c = st;
             cur.base = 0;
-            cur.w = w;
             load_batch(cur);
             Batch nxt = batch_after(cur);
             load_batch(nxt);
-            while (item < p.num_items && ok) {
-                const Item cw = w;
+            while (st.valid && ok) {
+                const Item cw = st.w;
                 const int ckk0 = kk0;
-                if (cur.item != item || ckk0 - cur.base >= kOffBatch) {  // this stage starts the next batch
+                if (cur.c.seq != st.seq || ckk0 - cur.base >= kOffBatch) {  // this stage starts the next batch
                     cur = nxt;
                     nxt = batch_after(cur);
                     load_batch(nxt);
@@ -543,9 +689,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 const int bidx = ckk0 - cur.base;
                 // advance to the next stage
                 kk0 += kKT;
-                if (kk0 >= w.nk) {
+                if (kk0 >= cw.nk) {
                     kk0 = 0;
-                    item = next_nonempty(item, w);
+                    advance(st);
                 }
 
                 const bool chunk1 = (2 * cw.y + 1) < p.gm_total;
@@ -614,8 +760,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             uint32_t idx = 0, slot = 0, abuf = 0, apar = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
-                const Item w = decode_item(p, item);
+            Walk wk;
+            wk.init(p);
+            Item w;
+            while (ok && wk.next(p, w)) {
                 if (w.nk == 0) continue;
                 const uint32_t accbuf = idx % kAccBufs;
                 if (idx >= (uint32_t)kAccBufs)
@@ -658,8 +806,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         const int row_in_block = quad * 32 + lane;
         uint32_t idx = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
-            const Item w = decode_item(p, item);
+        Walk wk;
+        wk.init(p);
+        Item w;
+        const bool leader = warp == kEpilogueWarp0 && lane == 0;
+        while (ok && wk.next(p, w)) {
             const int grow = w.y * 128 + row_in_block;
             uint16_t* out = p.out + (p.split_k > 1 ? (size_t)w.batch * p.M * p.N : (size_t)0);
             if (w.nk == 0) {
@@ -669,12 +820,90 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 }
                 continue;
             }
+            // A run that is only part of its range: the CTAs that share the range (c_first..c_last, in k
+            // order) leave their fp32 sums in their scratch slots and count themselves on the range's
+            // counter; whoever completes the count adds the sums up in k order, so the result does not
+            // depend on who that is, and writes the fp16 result.  Nobody waits for anybody.
+            int c_first = 0, c_last = 0, u0 = 0, arrived = 0;
+            if (w.partial) {
+                const int row = w.nt * p.row_blocks + w.y;
+                u0 = row * p.kt_total + w.batch * p.avg_kt;
+                int u1 = u0 + p.avg_kt;
+                if (u1 > (row + 1) * p.kt_total) u1 = (row + 1) * p.kt_total;
+                c_first = share_owner(p, u0);
+                c_last = share_owner(p, u1 - 1);
+                // Look at the counter while the MMAs of the run are still in flight: if all the others
+                // have arrived already (the usual case for a CTA's last run) this CTA completes the range
+                // straight from its registers, without publishing its own sums first.
+                if (leader) arrived = ld_acquire_gpu(p.counters + w.id);
+            }
             const uint32_t accbuf = idx % kAccBufs;
             ok = mbar_wait_relaxed(bar_accfull + 8 * accbuf, (idx / kAccBufs) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
+            bool direct = false;
+            if (w.partial) {
+                if (leader) {
+                    // the run may have been long: look again before taking the slower way
+                    if (arrived != c_last - c_first) arrived = ld_acquire_gpu(p.counters + w.id);
+                    *finisher = arrived == c_last - c_first;
+                }
+                // the four warps meet on a named barrier below, so they must agree to go on
+                ok = bar_and_epilogue(ok);
+                direct = *finisher != 0;
+            }
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + accbuf * (kNAcc * NPAD);
+            // the first contributor used its second slot unless its share starts with this range
+            const int slot_first = w.partial && share_begin(p, c_first) != u0 ? 1 : 0;
+            auto slot_of = [&](int cc) -> float* {
+                return p.partials + (size_t)(2 * cc + (cc == c_first ? slot_first : 0)) * (128 * NPAD) + row_in_block;
+            };
+            float* mine = slot_of((int)blockIdx.x);
+            // adds the sums of all contributors to acc in k order (own: the registers r when have_own)
+            auto add_all = [&](float* acc, const uint32_t* r, int c, bool have_own) {
+#pragma unroll 1
+                for (int cc = c_first; cc <= c_last; ++cc) {
+                    if (have_own && cc == (int)blockIdx.x) {
+#pragma unroll
+                        for (int n = 0; n < 16; ++n) acc[n] += __uint_as_float(r[n]);
+                    } else {
+                        const float* src = slot_of(cc) + c * 16 * 128;
+                        float v[16];
+#pragma unroll
+                        for (int n = 0; n < 16; ++n) v[n] = __ldcg(src + n * 128);
+#pragma unroll
+                        for (int n = 0; n < 16; ++n) acc[n] += v[n];
+                    }
+                }
+            };
+            // the same without own registers: two contributors' sums are fetched together
+            auto add_all_pairs = [&](float* acc, int c) {
+#pragma unroll 1
+                for (int cc = c_first; cc <= c_last; cc += 2) {
+                    const bool two = cc + 1 <= c_last;
+                    const float* s0 = slot_of(cc) + c * 16 * 128;
+                    const float* s1 = slot_of(two ? cc + 1 : cc) + c * 16 * 128;
+                    float v0[16], v1[16];
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) v0[n] = __ldcg(s0 + n * 128);
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) v1[n] = __ldcg(s1 + n * 128);
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) {
+                        acc[n] += v0[n];
+                        if (two) acc[n] += v1[n];
+                    }
+                }
+            };
+            auto write_out = [&](const float* acc, int c) {
+#pragma unroll
+                for (int n = 0; n < 16; ++n) {
+                    const int col = w.nt * NPAD + c * 16 + n;
+                    if (col < p.N && grow < p.M)
+                        out[(size_t)col * p.M + grow] = __half_as_ushort(__float2half_rn(acc[n]));
+                }
+            };
 #pragma unroll
             for (int c = 0; c < NPAD / 16; ++c) {
                 uint32_t r[16];
@@ -693,11 +922,46 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_accempty + 8 * accbuf);
                 }
+                if (!w.partial) {
+                    float acc[16];
 #pragma unroll
-                for (int n = 0; n < 16; ++n) {
-                    const int col = w.nt * NPAD + c * 16 + n;
-                    if (col < p.N && grow < p.M)
-                        out[(size_t)col * p.M + grow] = __half_as_ushort(__float2half_rn(__uint_as_float(r[n])));
+                    for (int n = 0; n < 16; ++n) acc[n] = __uint_as_float(r[n]);
+                    write_out(acc, c);
+                } else if (direct) {
+                    float acc[16];
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) acc[n] = 0.f;
+                    add_all(acc, r, c, true);
+                    write_out(acc, c);
+                } else {
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) __stcg(mine + (c * 16 + n) * 128, __uint_as_float(r[n]));
+                }
+            }
+            if (w.partial && direct) {
+                if (leader) p.counters[w.id] = 0;  // ready for the next launch
+            } else if (w.partial) {
+                // One thread publishes the CTA's partial sums (its fence covers the stores the barrier
+                // ordered before it) and counts the arrival; its second fence makes the other CTAs' sums
+                // visible to the threads that pass the second barrier.
+                bar_sync_epilogue();
+                if (leader) {
+                    __threadfence();
+                    const int before = atomicAdd(p.counters + w.id, 1);
+                    if (before == c_last - c_first) __threadfence();
+                    *finisher = before == c_last - c_first;
+                }
+                bar_sync_epilogue();
+                if (*finisher) {
+#pragma unroll 1
+                    for (int c = 0; c < NPAD / 16; ++c) {
+                        float acc[16];
+#pragma unroll
+                        for (int n = 0; n < 16; ++n) acc[n] = 0.f;
+                        add_all_pairs(acc, c);
+                        write_out(acc, c);
+                    }
+                    if (leader) p.counters[w.id] = 0;
                 }
             }
             ++idx;
@@ -712,31 +976,37 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         reg_alloc<kRegsDecode>();
         const int dw = warp - kDecodeWarp0;
         const int group = dw >> 2;
-        const int set = group / kKT, sub = group % kKT;
+        const int set = group / kKT, gsub = group % kKT;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;      // weight row inside the 128-row block
         const uint32_t lut = smem_u32(lut_tab);
         const int chunk = row >> 6, rr = row & 63;   // 64-row global-tile row of the block, row inside it
         const int r_in_tile = rr & 7;
         const uint32_t my_v = chunk ? off_v1 : off_v0;
-        const uint32_t my_mt = (chunk ? off_mt1 : off_mt0) + (uint32_t)sub * 16 + 4 * (uint32_t)(rr >> 4);
-        const uint32_t my_rel = off_rel + 4 * (uint32_t)(chunk * kKT + sub);
-        // bitmap of the first of the row's 8 tiles (they are 16 bytes apart): median tile rr >> 4, row half
-        // (rr >> 3) & 1 of the 2 x 2 tile order
-        const uint32_t sp_bm = (chunk ? off_bm1 : off_bm0) + (uint32_t)sub * 512 +
-                               8 * (uint32_t)(16 * (rr >> 4) + ((rr >> 3) & 1));
+        // k-tile 0 of a stage: this row's median offset, its global tile's start, and the bitmap of the first
+        // of the row's 8 tiles (they are 16 bytes apart): median tile rr >> 4, row half (rr >> 3) & 1 of
+        // the 2 x 2 tile order
+        const uint32_t mt0 = (chunk ? off_mt1 : off_mt0) + 4 * (uint32_t)(rr >> 4);
+        const uint32_t rel0 = off_rel + 4 * (uint32_t)(chunk * kKT);
+        const uint32_t bm0 = (chunk ? off_bm1 : off_bm0) + 8 * (uint32_t)(16 * (rr >> 4) + ((rr >> 3) & 1));
         const uint32_t below_lo = r_in_tile < 4 ? (1u << (8 * r_in_tile)) - 1u : 0xffffffffu;
         const uint32_t below_hi = r_in_tile <= 4 ? 0u : (1u << (8 * (r_in_tile - 4))) - 1u;
         const uint32_t rsel = 0x4440u | (uint32_t)r_in_tile;
         const uint32_t second = ((rr >> 3) & 1) ? 0xffffffffu : 0u;
 
         uint32_t slot = 0, round = 0, mine = 0;
+        // The k-tiles of the set's stages are dealt to its groups in turn, across stages and work items:
+        // k-tile j of a stage goes to group (j + rot) % kKT, rot = k-tiles dealt so far.  A stage with
+        // fewer than kKT k-tiles (the end of a work item) then costs no more than the k-tiles it has.
+        uint32_t rot = 0;
         int turn = 0;      // stage counter modulo kSets: this warp's set works when turn == set
         uint32_t abuf = (uint32_t)set;  // TMEM A buffer (in stages) of this set's next stage
         uint32_t bar_old = 0, par_old = 0, bar_new = 0, par_new = 0;  // empty barriers of this set's last two stages
         bool ok = true;
-        for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
-            const Item w = decode_item(p, item);
+        Walk wk;
+        wk.init(p);
+        Item w;
+        while (ok && wk.next(p, w)) {
             const bool chunk1 = (2 * w.y + 1) < p.gm_total;
             const bool valid = (chunk == 0) || chunk1;
             for (int kk0 = 0; kk0 < w.nk; kk0 += kKT) {
@@ -748,7 +1018,12 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     }
                     continue;
                 }
-                const bool active = sub < w.nk - kk0;  // this group's k-tile exists in the stage
+                const int nv = min(kKT, w.nk - kk0);
+                const int sub = (int)(((uint32_t)gsub + (uint32_t)kKT - rot) % (uint32_t)kKT);  // this group's k-tile
+                rot = (rot + (uint32_t)nv) % (uint32_t)kKT;
+                const bool active = sub < nv;  // ... exists in the stage
+                const uint32_t my_mt = mt0 + (uint32_t)sub * 16, my_rel = rel0 + 4 * (uint32_t)sub;
+                const uint32_t sp_bm = bm0 + (uint32_t)sub * 512;
                 ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -900,6 +1175,97 @@ DeviceInfo device_info()
     return cache[dev];
 }
 
+// ---------------------------------------------------------------- scratch of the balanced schedule
+// Owned by the library, one set per (device, stream) so that calls on different streams never share
+// counters; calls on one stream are ordered by the stream.  Created on the first eligible call of a
+// stream (cudaMalloc, so never while the stream is being captured; a captured call uses the set an
+// earlier call on the capturing stream created, else the static schedule).
+constexpr int kScratchSets = 8;
+constexpr int kCounterCap = 1 << 20;
+struct ScratchSet {
+    float* partials = nullptr;
+    int* counters = nullptr;
+    cudaStream_t stream = nullptr;
+    bool taken = false;
+};
+std::mutex g_scratch_mu;
+ScratchSet g_scratch[64][kScratchSets];
+std::atomic<int> g_schedule{0};       // 0: by the cost model, 1: always static, 2: balanced whenever possible
+thread_local int t_static_depth = 0;  // > 0: this thread's calls use the static schedule
+
+const ScratchSet* scratch_for(cudaStream_t st, int dev, int sms, bool may_create)
+{
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    ScratchSet* sets = g_scratch[dev];
+    for (int i = 0; i < kScratchSets; ++i)
+        if (sets[i].taken && sets[i].stream == st) return &sets[i];
+    if (!may_create) return nullptr;
+    for (int i = 0; i < kScratchSets; ++i) {
+        if (sets[i].taken) continue;
+        ScratchSet n;
+        const size_t pbytes = (size_t)2 * sms * 128 * 64 * sizeof(float);
+        if (cudaMalloc(&n.partials, pbytes) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        if (cudaMalloc(&n.counters, (size_t)kCounterCap * sizeof(int)) != cudaSuccess ||
+            cudaMemset(n.counters, 0, (size_t)kCounterCap * sizeof(int)) != cudaSuccess ||
+            cudaDeviceSynchronize() != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(n.partials);
+            if (n.counters) cudaFree(n.counters);
+            return nullptr;
+        }
+        n.stream = st;
+        n.taken = true;
+        sets[i] = n;
+        return &sets[i];
+    }
+    return nullptr;  // more streams than sets: the static schedule needs none
+}
+
+bool stream_is_capturing(cudaStream_t st)
+{
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        return true;  // e.g. the legacy stream while another stream captures: stay on the safe side
+    }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
+// Cost model of the two schedules, in units of one k-tile of one 128-row block on one SM (about 0.45 us),
+// fitted to timings of OPT-shaped matrices at N = 16 and 32.  Every work item after an SM's first costs
+// about 4 k-tiles (pipeline hand-over), a split-K reduction launch about 3.  The exchange of partial sums at
+// the end of a balanced kernel costs about 6 plus 2.2 per round of loads: one round per 16 columns and per
+// other SM that shares a range.
+double static_cost(int row_blocks, int n_tiles, int kt, int sk, int sms)
+{
+    const int avg = (kt - 1) / sk + 1;
+    const long items = (long)row_blocks * n_tiles * sk;
+    const long waves = (items + sms - 1) / sms;
+    return (double)waves * (avg + 4.0) - 4.0 + (sk > 1 ? 3.0 + 0.15 * sk : 0.0);
+}
+double balanced_cost(int row_blocks, int n_tiles, int kt, int sk, int sms, int npad)
+{
+    const double units = (double)row_blocks * n_tiles * kt;
+    const long items = (long)row_blocks * n_tiles * sk;
+    const int avg = (kt - 1) / sk + 1;
+    const double share = units / (units < sms ? units : sms);
+    const bool cuts = items % sms != 0 || avg * sk != kt;  // some range is shared between SMs
+    double exchange = 0.0;
+    if (cuts) {
+        double others = avg / share;
+        others = others <= 1.0 ? 1.0 : (double)(long)(others + 0.999);
+        exchange = 6.0 + 2.2 * (npad / 16) * others;
+    }
+    return share + exchange + (sk > 1 ? 3.0 + 0.15 * sk : 0.0);
+}
+bool prefer_balanced(int row_blocks, int n_tiles, int kt, int sk, int sms, int npad)
+{
+    return balanced_cost(row_blocks, n_tiles, kt, sk, sms, npad) < static_cost(row_blocks, n_tiles, kt, sk, sms);
+}
+
 template <int NPAD>
 cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, int* status)
 {
@@ -940,43 +1306,98 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     p.num_items = p.n_tiles * p.row_blocks * a.split_k;
     const int dyn_smem = di.max_smem - 1024;  // the kernel also has a small static table
     p.smem_bytes = (uint32_t)dyn_smem;
-
-    static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
+    // Balanced schedule: every CTA gets the same number of k-tiles; needs the library's scratch.
+    const long long units = (long long)p.n_tiles * p.row_blocks * p.kt_total;
+    const bool no_empty_range = (long long)(a.split_k - 1) * p.avg_kt < p.kt_total;
+    p.partials = nullptr;
+    p.counters = nullptr;
+    p.balanced = 0;
+    p.units = 0;
+    const int mode = g_schedule.load();
+    if (mode != 1 && t_static_depth == 0 && (units + 1) * di.sms < (1LL << 31) && p.num_items <= kCounterCap &&
+        no_empty_range && (mode == 2 || prefer_balanced(p.row_blocks, p.n_tiles, p.kt_total, a.split_k, di.sms, NPAD))) {
+        // While the stream is being captured nothing may be allocated: the scratch of an earlier call
+        // on this stream is used if there is one.
+        if (const ScratchSet* sc = scratch_for(s, dev, di.sms, !stream_is_capturing(s))) {
+            p.partials = sc->partials;
+            p.counters = sc->counters;
+            p.balanced = 1;
+            p.units = (int)units;
+        }
+    }
+
+    static bool attr_set[64] = {false};
     if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(spmm_bitmap_tcgen05_kernel<NPAD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    const int grid = p.num_items < di.sms ? p.num_items : di.sms;
-    spmm_bitmap_tcgen05_kernel<NPAD><<<grid, kThreads, dyn_smem, s>>>(p, tmap);
-    return cudaGetLastError();
+    const long long work = p.balanced ? units : (long long)p.num_items;
+    const int grid = work < di.sms ? (int)work : di.sms;
+    // Programmatic dependent launch: this kernel's set-up may overlap the end of the stream's previous
+    // kernel; the kernel itself waits for that kernel before it touches global memory.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = (size_t)dyn_smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, spmm_bitmap_tcgen05_kernel<NPAD>, p, tmap);
 }
 
 }  // namespace
 
+int set_schedule(int mode)
+{
+    if (mode < 0 || mode > 2) return -1;
+    return g_schedule.exchange(mode);
+}
+void push_static_schedule() { ++t_static_depth; }
+void pop_static_schedule() { --t_static_depth; }
+
+cudaError_t reset_schedule_scratch()
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    for (int i = 0; i < kScratchSets; ++i) {
+        if (!g_scratch[dev][i].taken) continue;
+        e = cudaMemset(g_scratch[dev][i].counters, 0, (size_t)kCounterCap * sizeof(int));
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
 int suggest_split_k(int M, int N, int K)
 {
-    (void)N;
     DeviceInfo di = device_info();
     const int sms = di.ok ? di.sms : 148;
     const int row_blocks = (M / 64 + 1) / 2;
     const int kt = K / 64;
+    const int n_tiles = N <= 64 ? 1 : (N + 63) / 64;
     if (row_blocks <= 0 || kt <= 0) return 1;
-    // Smallest split whose item count fills the SMs at least ~twice, while keeping each
-    // range at least 8 k-tiles long.
+    const bool may_balance = g_schedule.load() != 1 && t_static_depth == 0;
     int best = 1;
-    double best_cost = 1e30;
-    for (int sk = 1; sk <= 32 && sk <= kt; ++sk) {
+    double best_cost = static_cost(row_blocks, n_tiles, kt, 1, sms);
+    if (may_balance) {
+        // Split_K = 1 with equal shares needs no fp16 partial sums and no reduction
+        const double c = balanced_cost(row_blocks, n_tiles, kt, 1, sms, N <= 16 ? 16 : N <= 32 ? 32 : 64);
+        if (c < best_cost) best_cost = c;
+    }
+    for (int sk = 2; sk <= 32 && sk <= kt; ++sk) {
         const int avg = (kt - 1) / sk + 1;
         if ((sk - 1) * avg >= kt) continue;  // would leave an empty last range
-        if (avg < 4 && sk > 1) break;
-        const long items = (long)row_blocks * sk;
-        const long waves = (items + sms - 1) / sms;
-        // time ~ waves * (avg + fixed per-item overhead) ; + a small cost per extra partial
-        const double cost = (double)waves * (avg + 3.0) + 0.15 * sk;
+        if (avg < 4) break;
+        const double cost = static_cost(row_blocks, n_tiles, kt, sk, sms);
         if (cost < best_cost - 1e-9) {
             best_cost = cost;
             best = sk;

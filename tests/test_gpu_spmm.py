@@ -62,8 +62,77 @@ def _run(sp, A, B, split_k):
 def test_spmm_matches_fp32_oracle(sp, M, K, N, s, sk):
     A = make_sparse(M, K, s, seed=M + 3 * K + N)
     B = make_dense(N, K, seed=N + K, dist="uniform" if M == 4096 else "normal")
-    C = _run(sp, A, B, sk)
-    _assert_close(C, oracle.gemm_f32(A, B))
+    ref = oracle.gemm_f32(A, B)
+    for schedule in (sp.SCHEDULE_BALANCED, sp.SCHEDULE_STATIC):
+        prev = sp.set_schedule(schedule)
+        try:
+            C = _run(sp, A, B, sk)
+        finally:
+            sp.set_schedule(prev)
+        _assert_close(C, ref)
+    assert sp.device_status() == 0
+
+
+@pytest.mark.parametrize("M,K,N,s,sk", [
+    (5120, 5120, 16, 0.6, 1),     # 3200 k-tiles over the SMs: every range is cut between several SMs
+    (4096, 4096, 32, 0.5, 6),     # ranges of 11 k-tiles, shares of 13.8
+    (192, 64 * 40, 16, 0.5, 1),   # fewer k-tiles than SMs, half-filled last row block
+    (1024, 1024, 128, 0.5, 3),    # two activation tiles
+    (15360, 5120, 8, 0.6, 1),     # OPT-13B QKV
+])
+def test_balanced_schedule_repeatable_and_close_to_static(sp, M, K, N, s, sk):
+    """Equal k-tile shares per SM with the fp32 fix-up: the same bits on every call (the sums are taken in k
+    order whoever finishes last, and the arrival counters return to zero), and the static schedule's result
+    up to the order of the fp32 additions."""
+    A = make_sparse(M, K, s, seed=M + K + N + 5)
+    B = torch.from_numpy(make_dense(N, K, seed=N + K + 5)).cuda()
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    assert sp.set_schedule(sp.SCHEDULE_BALANCED) == sp.SCHEDULE_AUTO
+    try:
+        runs = [sp.spmm(W, B, split_k=sk).cpu().numpy() for _ in range(3)]
+        sp.set_schedule(sp.SCHEDULE_STATIC)
+        static = sp.spmm(W, B, split_k=sk).cpu().numpy()
+    finally:
+        sp.set_schedule(sp.SCHEDULE_AUTO)
+    assert np.array_equal(runs[0].view(np.uint16), runs[1].view(np.uint16))
+    assert np.array_equal(runs[0].view(np.uint16), runs[2].view(np.uint16))
+    scale = float(np.abs(static.astype(np.float32)).max())
+    assert float(np.abs(runs[0].astype(np.float32) - static.astype(np.float32)).max()) <= 2e-3 * scale
+    if M <= 5120:
+        _assert_close(runs[0], oracle.gemm_f32(A, B.cpu().numpy()))
+    assert sp.device_status() == 0
+
+
+def test_captured_calls_replay(sp):
+    """Calls captured into a CUDA graph after a warm-up call on the capturing stream (balanced schedule, the
+    stream's scratch exists) and on a stream that never ran one (static schedule): replays give the eager result."""
+    A = make_sparse(2048, 2048, 0.6, seed=21)
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    B = torch.from_numpy(make_dense(16, 2048, seed=22)).cuda()
+    eager = sp.spmm(W, B, split_k=1)
+    torch.cuda.synchronize()
+    sp.set_schedule(sp.SCHEDULE_BALANCED)
+    for warm in (True, False):
+        st = torch.cuda.Stream()
+        out = torch.zeros((16, 2048), dtype=torch.float16, device="cuda")
+        ws = torch.empty(2 * 16 * 2048, dtype=torch.float16, device="cuda")
+        if warm:
+            with torch.cuda.stream(st):
+                sp.spmm(W, B, split_k=1, out=out, stream=st)
+            st.synchronize()
+            out.zero_()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            sp.spmm(W, B, split_k=1, out=out, stream=st)
+            sp.spmm(W, B, split_k=2, out=out, workspace=ws, stream=st)
+            sp.spmm(W, B, split_k=1, out=out, stream=st)
+        for _ in range(3):
+            out.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            got, want = out.float(), eager.float()
+            assert float((got - want).abs().max()) <= 2e-3 * float(want.abs().max())
+    sp.set_schedule(sp.SCHEDULE_AUTO)
     assert sp.device_status() == 0
 
 

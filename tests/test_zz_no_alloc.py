@@ -36,7 +36,12 @@ def test_noalloc_entry_point_matches_regular_entry_point(lib_built):
         A = make_sparse(M, K, s, seed)
         B = torch.from_numpy(make_dense(N, K, seed + 100)).cuda()
         W = sp.encode_device(torch.from_numpy(A).cuda())
-        want = sp.spmm(W, B, split_k=sk)                      # regular entry point, caller-owned workspace
+        balanced = sp.spmm(W, B, split_k=sk)                  # regular entry point, caller-owned workspace
+        prev = sp.set_schedule(sp.SCHEDULE_STATIC)            # the schedule the allocation-free entry point uses
+        try:
+            want = sp.spmm(W, B, split_k=sk)
+        finally:
+            sp.set_schedule(prev)
         got = torch.full((N, M), float("nan"), dtype=torch.float16, device="cuda")
         code = lib.spb_spmm_bitmap_v3_noalloc(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
                                               ctypes.c_void_p(W.vals.data_ptr()), ctypes.c_void_p(W.gtile.data_ptr()),
@@ -46,7 +51,8 @@ def test_noalloc_entry_point_matches_regular_entry_point(lib_built):
         assert code == 0, _lib.last_error()
         torch.cuda.synchronize()
         assert _close(got.cpu().numpy(), want.cpu().numpy())
-        # same kernels, same split: the two paths are in fact bit-identical
+        assert _close(got.cpu().numpy(), balanced.cpu().numpy())
+        # same kernels, same split, same schedule: the two paths are in fact bit-identical
         assert np.array_equal(got.cpu().numpy().view(np.uint16), want.cpu().numpy().view(np.uint16))
     assert sp.device_status() == 0
 
