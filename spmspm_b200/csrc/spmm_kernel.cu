@@ -47,7 +47,7 @@ namespace {
 constexpr int kKT = SPB_KT;
 constexpr int kDecodeGroups = 4;
 constexpr int kSets = kDecodeGroups / kKT;
-static_assert(kKT * kSets == kDecodeGroups, "kKT must be 1, 2 or 4");
+static_assert(kKT == 4 && kSets == 1, "the decode loop deals the k-tiles of a stage to all four groups");
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
@@ -64,7 +64,7 @@ static_assert(128 * kRegsControl + 128 * kRegsEpilogue + 128 * kDecodeGroups * k
 static_assert(kRegsControl <= kRegsLaunch && kRegsEpilogue <= kRegsLaunch && kRegsDecode >= kRegsLaunch,
               "roles that shrink must not exceed, roles that grow must not undercut the launch allocation");
 constexpr int kMaxStages = 24;
-constexpr int kHeaderBytes = 1024;
+constexpr int kHeaderBytes = 3072;  // barriers and flags (1 KB), then 128 bytes of tile starts per decode warp
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 
@@ -427,9 +427,13 @@ __device__ __forceinline__ void lds64(uint32_t addr, uint32_t& a, uint32_t& b)
 // value and positions 4-7 from a 4-value window ending at its last value.  Every output register
 // (two positions) is one permute of a 2-value window and a zero register:
 //   pair_sel(lo, hi, first): selector placing the window's values at the kept positions.
-// Low-nibble entry  {sel(pos 0,1) | window(pos 2,3) << 16, sel(pos 2,3)}
-// High-nibble entry {sel(pos 6,7) | window(pos 4,5) << 16, sel(pos 4,5)}
-// where window(...) is the permute selector that cuts the 2-value window out of the 4-value one.
+// Low-nibble entry  sel(pos 0,1) | sel(pos 2,3) << 16
+// High-nibble entry sel(pos 6,7) | sel(pos 4,5) << 16
+// The 2-value window of positions 2,3 starts (number of values at positions 0,1) values into the 4-value
+// window, the one of positions 4,5 ends (number of values at positions 6,7) values before its end; the
+// permute selectors that cut them out are computed from those counts.  The tables are kept to 32-bit
+// entries because the decode warps are bound by shared-memory wavefronts, not by arithmetic: a 4-byte load
+// from a 64-byte table is one conflict-free wavefront, an 8-byte one at least two.
 __device__ __forceinline__ uint32_t pair_sel_bottom(uint32_t lo, uint32_t hi)
 {
     // window = {next value, the one after}; zero register in bytes 4..7
@@ -444,17 +448,15 @@ __device__ __forceinline__ uint32_t pair_sel_top(uint32_t lo, uint32_t hi)
     const uint32_t p_lo = lo ? (hi ? 0x10u : 0x32u) : 0x54u;
     return p_lo | (p_hi << 8);
 }
-__device__ __forceinline__ uint2 lut_low_entry(uint32_t n)
+__device__ __forceinline__ uint32_t lut_low_entry(uint32_t n)
 {
     const uint32_t b0 = n & 1, b1 = (n >> 1) & 1, b2 = (n >> 2) & 1, b3 = (n >> 3) & 1;
-    const uint32_t win = 0x3210u + 0x2222u * (b0 + b1);  // values b0+b1, b0+b1+1 of the 4-value window
-    return make_uint2(pair_sel_bottom(b0, b1) | (win << 16), pair_sel_bottom(b2, b3));
+    return pair_sel_bottom(b0, b1) | (pair_sel_bottom(b2, b3) << 16);
 }
-__device__ __forceinline__ uint2 lut_high_entry(uint32_t n)
+__device__ __forceinline__ uint32_t lut_high_entry(uint32_t n)
 {
     const uint32_t b4 = n & 1, b5 = (n >> 1) & 1, b6 = (n >> 2) & 1, b7 = (n >> 3) & 1;
-    const uint32_t win = 0x3210u + 0x2222u * (2 - (b6 + b7));  // the two values before those of pos 6,7
-    return make_uint2(pair_sel_top(b6, b7) | (win << 16), pair_sel_top(b4, b5));
+    return pair_sel_top(b6, b7) | (pair_sel_top(b4, b5) << 16);
 }
 
 // Expansion of one 8-element row segment (one row of one 8x8 tile) into 4 registers of packed fp16,
@@ -465,7 +467,7 @@ __device__ __forceinline__ uint2 lut_high_entry(uint32_t n)
 #endif
 constexpr int kUnitBatch = SPB_UNIT_BATCH;  // row segments whose loads are issued together (1, 2 or 4)
 struct UnitLoads {
-    uint32_t x0, x1, x2, y0, y1, y2, l0, l1, h0, h1, sb, st;
+    uint32_t x0, x1, x2, y0, y1, y2, l, h, c01, c67, sb, st;
 };
 __device__ __forceinline__ void lds32x3_before(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c)
 {
@@ -473,28 +475,22 @@ __device__ __forceinline__ void lds32x3_before(uint32_t addr, uint32_t& a, uint3
                  : "=&r"(a), "=&r"(b), "=&r"(c)
                  : "r"(addr));
 }
-// Load half: everything a row segment needs is derived from the tile's 64-bit bitmap (lo, hi)
-// in the thread that expands it.  `run` is the shared address where the values of this tile *pair*
-// (the tile of rows 0-7 and the one of rows 8-15 of the same 16-row median tile and 8-column slice)
-// start; it is advanced past the pair.  The other tile's count comes from the lane 8 away.
+// Load half for one row segment.  lo, hi: the 64-bit bitmap of the segment's tile; tile: shared address of
+// the tile's first value.
 //   below_lo/below_hi  thread constants: bitmap bits of the tile rows above this thread's row
 //   rsel               permute selector moving this row's mask byte to byte 0
-//   second             all ones in the threads of the second tile of the pair, else zero
-__device__ __forceinline__ void unit_load_sp(uint32_t lo, uint32_t hi, uint32_t& run, uint32_t below_lo,
-                                             uint32_t below_hi, uint32_t rsel, uint32_t second, uint32_t lut,
-                                             UnitLoads& u)
+__device__ __forceinline__ void unit_load(uint32_t lo, uint32_t hi, uint32_t tile, uint32_t below_lo,
+                                          uint32_t below_hi, uint32_t rsel, uint32_t lut, UnitLoads& u)
 {
-    const uint32_t cnt = __popc(lo) + __popc(hi);
-    const uint32_t other = __shfl_xor_sync(0xffffffffu, cnt, 8);
-    const uint32_t tile = run + 2u * (other & second);
-    run += 2u * (cnt + other);
     const uint32_t w0 = tile + 2u * (__popc(lo & below_lo) + __popc(hi & below_hi));
     const uint32_t g = prmt(lo, hi, rsel);                 // row mask in byte 0 (bytes 1-3 are not clean)
     const uint32_t wt = w0 + 2u * __popc(g & 0xffu);       // address just past the row's last value
     lds32x3(w0 & ~3u, u.x0, u.x1, u.x2);
     lds32x3_before(wt & ~3u, u.y0, u.y1, u.y2);            // window of the 4 values before wt
-    lds64(lut + (g & 15u) * 8u, u.l0, u.l1);
-    lds64(lut + 128u + (g & 0xf0u), u.h0, u.h1);           // high-nibble entries are 16 bytes apart
+    u.l = lds32(lut + (g & 15u) * 4u);
+    u.h = lds32(lut + 64u + ((g >> 2) & 0x3cu));
+    u.c01 = __popc(g & 3u);                                // values at positions 0,1
+    u.c67 = __popc(g & 0xc0u);                             // values at positions 6,7
     u.sb = w0 << 3;
     u.st = wt << 3;
 }
@@ -502,19 +498,19 @@ __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
 {
     const uint32_t b0 = __funnelshift_r(u.x0, u.x1, u.sb), b1 = __funnelshift_r(u.x1, u.x2, u.sb);
     const uint32_t t0 = __funnelshift_r(u.y0, u.y1, u.st), t1 = __funnelshift_r(u.y1, u.y2, u.st);
-    o[0] = prmt(b0, 0u, u.l0);
-    o[1] = prmt(prmt(b0, b1, u.l0 >> 16), 0u, u.l1);
-    o[2] = prmt(prmt(t0, t1, u.h0 >> 16), 0u, u.h1);
-    o[3] = prmt(t1, 0u, u.h0);
+    const uint32_t win_lo = 0x3210u + 0x2222u * u.c01, win_hi = 0x7654u - 0x2222u * u.c67;
+    o[0] = prmt(b0, 0u, u.l);
+    o[1] = prmt(prmt(b0, b1, win_lo), 0u, u.l >> 16);
+    o[2] = prmt(prmt(t0, t1, win_hi), 0u, u.h >> 16);
+    o[3] = prmt(t1, 0u, u.h);
 }
 
 template <int NPAD>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtensorMap tmap_b)
 {
-    // selector tables: low nibble entries [0,16); high nibble entry n at index 16 + 2n (16 bytes apart,
-    // so that the nibble's bit position can be used as the offset)
-    __shared__ __align__(16) uint2 lut_tab[48];
+    // selector tables: low nibble entries [0,16), high nibble entries [16,32)
+    __shared__ __align__(128) uint32_t lut_tab[32];
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled activation tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -525,10 +521,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t bar_full = smem_u32(bars);                         // [kMaxStages]
     const uint32_t bar_empty = bar_full + 8 * kMaxStages;             // [kMaxStages]
-    const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [2 * kSets]
-    const uint32_t bar_accfull = bar_aready + 8 * 2 * kSets;          // [2]
+    const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [2 * kKT]: A operand (buffer, k-tile) written
+    const uint32_t bar_afree = bar_aready + 8 * 2 * kKT;              // [2 * kKT]: ... read by its MMAs
+    const uint32_t bar_accfull = bar_afree + 8 * 2 * kKT;             // [2]
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kSets + 4));
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 4 * kKT + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     volatile int* finisher = reinterpret_cast<volatile int*>(tmem_holder + 2);
     const uint32_t stage0 = smem_u32(smem + kHeaderBytes);
@@ -548,7 +545,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             mbar_init(bar_full + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, 4 * kKT + 1);  // every decode warp + the MMA commit
         }
-        for (int i = 0; i < 2 * kSets; ++i) mbar_init(bar_aready + 8 * i, 4 * kKT);
+        for (int i = 0; i < 2 * kKT; ++i) {
+            mbar_init(bar_aready + 8 * i, 4);  // the four warps of the group that expanded the k-tile
+            mbar_init(bar_afree + 8 * i, 1);   // the commit after the k-tile's MMAs
+        }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_accfull + 8 * i, 1);
             mbar_init(bar_accempty + 8 * i, 4);
@@ -558,12 +558,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     }
     if (threadIdx.x >= 32 && threadIdx.x < 64) {
         const uint32_t n = threadIdx.x - 32;
-        if (n < 16) {
-            lut_tab[n] = lut_low_entry(n);
-        } else {
-            lut_tab[16 + 2 * (n - 16)] = lut_high_entry(n - 16);
-            lut_tab[17 + 2 * (n - 16)] = make_uint2(0u, 0u);
-        }
+        lut_tab[n] = n < 16 ? lut_low_entry(n) : lut_high_entry(n - 16);
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
@@ -603,13 +598,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     if (S > kMaxStages) S = kMaxStages;
 
 
-    // The A operands of n_abuf stages live in TMEM: two per set when the ring is deep enough, else one.
-    // A decode warp may overwrite a buffer once the MMAs of the stage n_abuf back have completed, which
-    // it learns from that stage's empty barrier; with a ring no deeper than n_abuf the full barrier of
-    // its own stage already implies it.
-    const uint32_t n_abuf = S > 2 * kSets ? 2u * kSets : (uint32_t)kSets;
-    const bool reuse_wait = (uint32_t)S > n_abuf;
-    const bool two_deep = n_abuf == 2u * kSets;
+    // The A operands of two stages live in TMEM (buffer = stage parity), one 32-column block per k-tile.
+    // Every block has its own pair of barriers: aready (the group that expanded the k-tile has written it)
+    // and afree (the MMAs that read it have completed), so that a decode group only ever waits for the
+    // tensor core's work on its own k-tiles, never for another group.  Which phase of a block's barriers
+    // comes next is kept as one bit per block (ph) by everybody who walks the stage sequence.
     if (S < 1) {
         // A single stage does not fit (cannot happen with the launch configuration used by the host
         // code); leave cleanly.
@@ -752,13 +745,13 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         } else if (warp == kMmaWarp) {
             // ================================================================= MMA issuer
             // The whole warp runs the loop with warp-uniform state (so addresses and descriptors stay
-            // in uniform registers); one elected lane issues.  A stage's A operands are ready when all
-            // decode warps have arrived on aready; they only arrive after the stage's full barrier
-            // completed, so the activation tiles have landed too.  One commit per stage arrives on
-            // its empty barrier: the producer may refill the stage and the decode warps may
-            // overwrite the TMEM A buffers.
+            // in uniform registers); one elected lane issues.  A k-tile's A operand is ready when the four
+            // warps of its group have arrived on its aready barrier; they only arrive after the stage's
+            // full barrier completed, so the activation tile has landed too.  A commit per k-tile tells
+            // the decode groups that the block may be rewritten; the last one of a stage also arrives on
+            // the stage's empty barrier, for the producers.
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            uint32_t idx = 0, slot = 0, abuf = 0, apar = 0;
+            uint32_t idx = 0, slot = 0, abuf = 0, ph = 0;
             bool ok = true;
             Walk wk;
             wk.init(p);
@@ -772,27 +765,27 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 const uint32_t d_tmem = tmem_base + accbuf * (kNAcc * NPAD);
                 for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT) {
                     const int nv = min(kKT, w.nk - kk0);
-                    ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_aready + 8 * abuf, apar, abort_flag));
-                    if (!ok) break;
-                    tc_fence_after();
                     const uint32_t sbase = stage0 + slot * stage_bytes;
-                    if (elect_one()) {
-                        for (int sub = 0; sub < nv; ++sub) {
+                    for (int sub = 0; sub < nv && ok; ++sub) {
+                        const uint32_t blk = abuf * kKT + (uint32_t)sub;
+                        ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_aready + 8 * blk, (ph >> blk) & 1u, abort_flag));
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (elect_one()) {
                             const uint64_t bdesc = make_b_desc(sbase + (uint32_t)sub * kBTile);
-                            const uint32_t a_tmem = tmem_a0 + (abuf * kKT + (uint32_t)sub) * 32;
+                            const uint32_t a_tmem = tmem_a0 + blk * 32;
 #pragma unroll
                             for (int s = 0; s < 4; ++s)
                                 tc_mma_ts(d_tmem + (s % kNAcc) * NPAD, a_tmem + 8 * s, bdesc + 2 * s, idesc,
                                           (kk0 > 0 || sub > 0 || s >= kNAcc) ? 1u : 0u);
+                            tc_commit(bar_afree + 8 * blk);
+                            if (sub == nv - 1) tc_commit(bar_empty + 8 * slot);
                         }
-                        tc_commit(bar_empty + 8 * slot);
+                        __syncwarp();
                     }
-                    __syncwarp();
+                    ph ^= ((1u << nv) - 1u) << (abuf * kKT);
                     if (++slot == (uint32_t)S) slot = 0;
-                    if (++abuf == n_abuf) {
-                        abuf = 0;
-                        apar ^= 1u;
-                    }
+                    abuf ^= 1u;
                 }
                 if (ok && elect_one()) tc_commit(bar_accfull + 8 * accbuf);
                 __syncwarp();
@@ -986,131 +979,109 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         // k-tile 0 of a stage: this row's median offset, its global tile's start, and the bitmap of the first
         // of the row's 8 tiles (they are 16 bytes apart): median tile rr >> 4, row half (rr >> 3) & 1 of
         // the 2 x 2 tile order
-        const uint32_t mt0 = (chunk ? off_mt1 : off_mt0) + 4 * (uint32_t)(rr >> 4);
         const uint32_t rel0 = off_rel + 4 * (uint32_t)(chunk * kKT);
         const uint32_t bm0 = (chunk ? off_bm1 : off_bm0) + 8 * (uint32_t)(16 * (rr >> 4) + ((rr >> 3) & 1));
+        // Lane l also looks after one of the 32 tiles of the warp's two median tiles per k-tile (tile l & 15 of
+        // median tile 2 * (quad & 1) + (l >> 4)): it works out where the tile's values start and leaves that in
+        // the warp's table, from which the row threads read the starts of the tiles they cross.
+        const uint32_t tile_tab = smem_u32(smem + 1024) + (uint32_t)dw * 128;
+        const uint32_t tile_bm0 = (chunk ? off_bm1 : off_bm0) + 8 * (uint32_t)(32 * (quad & 1) + lane);
+        const uint32_t tile_mt0 = (chunk ? off_mt1 : off_mt0) + 4 * (uint32_t)(2 * (quad & 1) + (lane >> 4));
+        const uint32_t tile_sel = 4 * (uint32_t)(16 * (lane >> 4) + ((lane >> 3) & 1));  // offset inside a table
         const uint32_t below_lo = r_in_tile < 4 ? (1u << (8 * r_in_tile)) - 1u : 0xffffffffu;
         const uint32_t below_hi = r_in_tile <= 4 ? 0u : (1u << (8 * (r_in_tile - 4))) - 1u;
         const uint32_t rsel = 0x4440u | (uint32_t)r_in_tile;
-        const uint32_t second = ((rr >> 3) & 1) ? 0xffffffffu : 0u;
 
-        uint32_t slot = 0, round = 0, mine = 0;
-        // The k-tiles of the set's stages are dealt to its groups in turn, across stages and work items:
-        // k-tile j of a stage goes to group (j + rot) % kKT, rot = k-tiles dealt so far.  A stage with
-        // fewer than kKT k-tiles (the end of a work item) then costs no more than the k-tiles it has.
-        uint32_t rot = 0;
-        int turn = 0;      // stage counter modulo kSets: this warp's set works when turn == set
-        uint32_t abuf = (uint32_t)set;  // TMEM A buffer (in stages) of this set's next stage
-        uint32_t bar_old = 0, par_old = 0, bar_new = 0, par_new = 0;  // empty barriers of this set's last two stages
+        // The k-tiles of the stages are dealt to the groups in turn, across stages and work items: k-tile j of
+        // a stage goes to group (j + rot) % kKT, rot = k-tiles dealt so far.  A stage with fewer than kKT
+        // k-tiles (the end of a work item) then costs no more than the k-tiles it has.
+        uint32_t slot = 0, round = 0, rot = 0, abuf = 0, ph = 0, used = 0;
+        const uint32_t tsel = tile_tab + tile_sel;
+#ifndef SPB_STAGGER_NS
+#define SPB_STAGGER_NS 450
+#endif
+        // The start of a k-tile (barrier checks, tile starts) is a chain of dependent instructions, its body
+        // is bound by arithmetic throughput.  Groups that start together stay together, all waiting and then
+        // all computing; started a quarter of a k-tile's time apart, one group's waiting overlaps the others'
+        // arithmetic on every scheduler, and nothing in the protocol pulls them back together.
+        if (gsub > 0) __nanosleep((unsigned)(SPB_STAGGER_NS * gsub));
         bool ok = true;
         Walk wk;
         wk.init(p);
         Item w;
         while (ok && wk.next(p, w)) {
-            const bool chunk1 = (2 * w.y + 1) < p.gm_total;
-            const bool valid = (chunk == 0) || chunk1;
-            for (int kk0 = 0; kk0 < w.nk; kk0 += kKT) {
-                if (turn != set) {  // another set's stage: only follow the ring
-                    if (++turn == kSets) turn = 0;
-                    if (++slot == (uint32_t)S) {
-                        slot = 0;
-                        ++round;
-                    }
-                    continue;
-                }
+            const bool valid = chunk == 0 || (2 * w.y + 1) < p.gm_total;
+            for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT) {
                 const int nv = min(kKT, w.nk - kk0);
                 const int sub = (int)(((uint32_t)gsub + (uint32_t)kKT - rot) % (uint32_t)kKT);  // this group's k-tile
                 rot = (rot + (uint32_t)nv) % (uint32_t)kKT;
-                const bool active = sub < nv;  // ... exists in the stage
-                const uint32_t my_mt = mt0 + (uint32_t)sub * 16, my_rel = rel0 + 4 * (uint32_t)sub;
-                const uint32_t sp_bm = bm0 + (uint32_t)sub * 512;
+                const uint32_t blk = abuf * kKT + (uint32_t)sub;
+                // Every group, with or without a k-tile, waits for the stage: it arrives on the stage's empty
+                // barrier below and must not get a ring round ahead of it.
                 ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
+                if (ok && sub < nv && ((used >> blk) & 1u))  // the MMAs of the block's previous k-tile
+                    ok = mbar_wait(bar_afree + 8 * blk, ((ph >> blk) & 1u) ^ 1u, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const uint32_t st = stage0 + slot * stage_bytes;
-                uint32_t a[32];
-                if (active) {
-                    // ---- thread <-> weight row.  Per batch of row segments: the bitmaps of their tiles, each
-                    // tile's start (running sum over the median tile), the row's start, the expansion, and
-                    // the store of the finished registers to tensor memory.
-                    bool fr = true;  // the TMEM A buffer may be rewritten once the MMAs that read it have completed
-                    if (reuse_wait) {
-                        if (two_deep) {
-                            if (mine >= 2) fr = mbar_wait(bar_old, par_old, abort_flag);
-                        } else if (mine >= 1) {
-                            fr = mbar_wait(bar_new, par_new, abort_flag);
+                if (sub < nv) {
+                    tc_fence_after();
+                    const uint32_t st = stage0 + slot * stage_bytes;
+                    {   // starts of the warp's 32 tiles: running sum of the tile sizes inside each median tile
+                        uint32_t lo = 0u, hi = 0u, base = st + my_v;
+                        if (valid) {
+                            lds64(st + tile_bm0 + (uint32_t)sub * 512, lo, hi);
+                            const uint32_t mt = lds32(st + tile_mt0 + (uint32_t)sub * 16);
+                            const uint32_t rel = lds32(st + rel0 + 4 * (uint32_t)sub);
+                            // clamped so that corrupt offsets can never point outside the stage
+                            base += min(rel + 2 * mt, (uint32_t)kKT * vmax);
                         }
-                    }
-                    fr = __all_sync(0xffffffffu, fr);
-                    const uint32_t ta = tmem_a0 + (abuf * kKT + (uint32_t)sub) * 32 + ((uint32_t)(quad * 32) << 16);
-                    if (fr) tc_fence_after();
-                    uint32_t run = st + my_v;
-                    if (valid) {
-                        const uint32_t mt = lds32(st + my_mt), rel = lds32(st + my_rel);
-                        // clamped so that corrupt offsets can never point outside the stage
-                        run += min(rel + 2 * mt, (uint32_t)kKT * vmax);
-                    }
+                        const uint32_t cnt = __popc(lo) + __popc(hi);
+                        uint32_t x = cnt;
 #pragma unroll
-                    for (int q0 = 0; q0 < 8; q0 += kUnitBatch) {
-                        uint32_t blo[kUnitBatch], bhi[kUnitBatch];
-                        UnitLoads u[kUnitBatch];
+                        for (int d = 1; d < 16; d <<= 1) {
+                            const uint32_t y = __shfl_up_sync(0xffffffffu, x, d, 16);
+                            if ((lane & 15) >= d) x += y;
+                        }
+                        __syncwarp();  // every lane has read the previous k-tile's table
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile_tab + 4 * (uint32_t)lane), "r"(base + 2 * (x - cnt))
+                                     : "memory");
+                        __syncwarp();
+                    }
+                    const uint32_t ta = tmem_a0 + blk * 32 + ((uint32_t)(quad * 32) << 16);
+                    const uint32_t sp_bm = st + bm0 + (uint32_t)sub * 512;
+                    uint32_t a[32];
 #pragma unroll
-                        for (int q = 0; q < kUnitBatch; ++q) {
+                    for (int q0 = 0; q0 < 8; q0 += 2) {
+                        uint32_t blo[2], bhi[2];
+                        UnitLoads u[2];
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
                             blo[q] = bhi[q] = 0u;
-                            if (valid) lds64(st + sp_bm + 16 * (q0 + q), blo[q], bhi[q]);
+                            if (valid) lds64(sp_bm + 16 * (q0 + q), blo[q], bhi[q]);
                         }
 #pragma unroll
-                        for (int q = 0; q < kUnitBatch; ++q)
-                            unit_load_sp(blo[q], bhi[q], run, below_lo, below_hi, rsel, second, lut, u[q]);
+                        for (int q = 0; q < 2; ++q)
+                            unit_load(blo[q], bhi[q], lds32(tsel + 8 * (q0 + q)), below_lo, below_hi, rsel, lut, u[q]);
 #pragma unroll
-                        for (int q = 0; q < kUnitBatch; ++q) unit_expand(u[q], a + 4 * (q0 + q));
-                        if (fr) {
-                            if (kUnitBatch == 4) {
-                                tc_st_32x32b_x16(ta + 4 * q0, a + 4 * q0);
-                            } else if (kUnitBatch == 2) {
-                                tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
-                            } else if (q0 & 1) {
-                                tc_st_32x32b_x8(ta + 4 * (q0 - 1), a + 4 * (q0 - 1));
-                            }
-                        }
+                        for (int q = 0; q < 2; ++q) unit_expand(u[q], a + 4 * (q0 + q));
+                        tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
                     }
-                    if (fr) {
-                        tc_wait_st();
-                        tc_fence_before();
-                    }
-                    ok = fr;
-                } else {
-                    // A group without a k-tile in this stage still arrives on aready.  Arrivals are
-                    // not tagged with a phase, so it must not run ahead of the stage two back either:
-                    // an early arrival would complete that stage's aready phase in place of a warp
-                    // that is still decoding.
-                    if (reuse_wait) {
-                        if (two_deep) {
-                            if (mine >= 2) ok = mbar_wait(bar_old, par_old, abort_flag);
-                        } else if (mine >= 1) {
-                            ok = mbar_wait(bar_new, par_new, abort_flag);
-                        }
-                    }
-                    ok = __all_sync(0xffffffffu, ok);
+                    tc_wait_st();
+                    tc_fence_before();
                 }
                 __syncwarp();
-                if (lane == 0 && ok) {
-                    mbar_arrive(bar_aready + 8 * abuf);
+                if (lane == 0) {
+                    if (sub < nv) mbar_arrive(bar_aready + 8 * blk);
                     mbar_arrive(bar_empty + 8 * slot);
                 }
-                bar_old = bar_new;
-                par_old = par_new;
-                bar_new = bar_empty + 8 * slot;
-                par_new = round & 1;
-                ++mine;
-                abuf += kSets;
-                if (abuf >= n_abuf) abuf -= n_abuf;
-                if (++turn == kSets) turn = 0;
+                const uint32_t mask = ((1u << nv) - 1u) << (abuf * kKT);
+                used |= mask;
+                ph ^= mask;
+                abuf ^= 1u;
                 if (++slot == (uint32_t)S) {
                     slot = 0;
                     ++round;
                 }
-                if (!ok) break;
             }
         }
     }
