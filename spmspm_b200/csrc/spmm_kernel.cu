@@ -8,21 +8,28 @@
 //                   1-D bulk copies and the activation tile with a 2-D TMA load into a ring of
 //                   shared-memory stages of four k-tiles each, completion on mbarriers;
 //   decode warps    (4 groups of 4 warps, one group per k-tile of a stage, one thread per weight
-//                   row) expand the bitmaps in a single pass: each thread reads the bitmaps of
-//                   the 8 tiles its row crosses, keeps a running sum of the tile sizes of its
-//                   median tile, finds its row's values with popcounts, expands them with byte
-//                   permutes driven by two nibble tables and writes the dense 128 x 64 fp16 tile
-//                   straight into tensor memory (tcgen05.st) as the MMA's A operand;
-//   MMA warp        one thread issues tcgen05.mma (M=128, N=16..128, K=16, fp16 in,
+//                   row) expand the bitmaps: per k-tile a warp first works out where the values of
+//                   its 32 tiles start (one tile per lane: population count of the bitmap, prefix
+//                   sum over the 16 tiles of a median tile by shuffles), then every thread, for
+//                   each of the 8 tiles its row crosses, finds its row's values with population
+//                   counts, expands them with byte permutes driven by two nibble tables and writes
+//                   the dense 128 x 64 fp16 tile straight into tensor memory (tcgen05.st) as the
+//                   MMA's A operand.  Every k-tile's A operand block has its own ready/free
+//                   barriers, so a group only ever waits for the tensor core's work on its own
+//                   k-tiles;
+//   MMA warp        one thread issues tcgen05.mma (M=128, N=16..64, K=16, fp16 in,
 //                   fp32 accumulate in TMEM), A from TMEM, B from the swizzled smem tile;
 //   epilogue warps  read the accumulator (tcgen05.ld), round to fp16 and store C or the
 //                   split-K partial, column-major as the reference does
 //                   (reference csrc/SpMM_Kernel.cuh:192-198).
 //
-// Work item = (row block of 128 rows, split-K range); the split-K ranges are cut exactly
-// like the reference's (reference csrc/SpMM_Kernel.cuh:35-43).  Every wait is bounded: when
-// one runs out the CTA records it in the device status word and leaves without touching
-// tensor memory again.
+// Work is scheduled in one of two ways (see Walk).  Static: a work item is (row block of 128 rows,
+// split-K range), the ranges cut exactly like the reference's (reference csrc/SpMM_Kernel.cuh:35-43),
+// items dealt to the CTAs round-robin.  Balanced: all k-tiles of all items are laid end to end and
+// every CTA takes an equal share; a range that is cut between CTAs is summed in fp32 through scratch
+// memory, by whichever of its CTAs finishes last, without anybody waiting.  Every wait in the kernel is
+// bounded: when one runs out the CTA records it in the device status word and leaves without
+// touching tensor memory again.
 #include "common.cuh"
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -37,17 +44,12 @@ namespace {
 //   warpgroup 0: warp 1 MMA issuer, warps 0, 2, 3 producers (each issues a share of the copies)
 //   warpgroup 1: epilogue (one warp per TMEM lane quadrant)
 //   warpgroup 2..: decode groups (one warp per quadrant each)
-#ifndef SPB_KT
-#define SPB_KT 4
-#endif
-// A pipeline stage holds kKT consecutive k-tiles of one 128-row block.  The four decode groups are
-// split into kSets sets of kKT groups; set s expands the stages s, s + kSets, ..., one group per k-tile.
-// Smaller stages mean more stages in the shared-memory ring (the loop producer -> HBM -> decode ->
-// MMA -> release is latency-bound), larger ones mean fewer copies per byte.
-constexpr int kKT = SPB_KT;
+// A pipeline stage holds kKT consecutive k-tiles of one 128-row block, one for each of the four decode
+// groups.  (Stages of one or two k-tiles mean more stages in the shared-memory ring and more copies per
+// byte; they measured 1.7x and 1.15x slower.)
+constexpr int kKT = 4;
 constexpr int kDecodeGroups = 4;
-constexpr int kSets = kDecodeGroups / kKT;
-static_assert(kKT == 4 && kSets == 1, "the decode loop deals the k-tiles of a stage to all four groups");
+static_assert(kKT == kDecodeGroups, "the decode loop deals the k-tiles of a stage to all groups");
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
@@ -380,15 +382,6 @@ struct Walk {
     }
 };
 
-__device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t* r)
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
-            taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
 // prmt.b32 in its default mode: selector nibble bits 2:0 pick one of the 8 source bytes, bit 3
 // replaces the byte by 8 copies of its sign bit.
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
@@ -462,10 +455,6 @@ __device__ __forceinline__ uint32_t lut_high_entry(uint32_t n)
 // Expansion of one 8-element row segment (one row of one 8x8 tile) into 4 registers of packed fp16,
 // split into a load half and a compute half so that the loads of several segments can be in flight
 // together.  lut: shared address of the selector tables.
-#ifndef SPB_UNIT_BATCH
-#define SPB_UNIT_BATCH 2
-#endif
-constexpr int kUnitBatch = SPB_UNIT_BATCH;  // row segments whose loads are issued together (1, 2 or 4)
 struct UnitLoads {
     uint32_t x0, x1, x2, y0, y1, y2, l, h, c01, c67, sb, st;
 };
@@ -536,7 +525,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     constexpr int kNAcc = 4;
     constexpr int kAccBufs = NPAD <= 32 ? 2 : 1;
     constexpr uint32_t kAccCols = kAccBufs * kNAcc * NPAD;
-    constexpr uint32_t kACols = 2 * kSets * kKT * 32;  // A operands of two stages per set
+    constexpr uint32_t kACols = 2 * kKT * 32;  // A operands of two stages
     static_assert(kAccCols + kACols <= 512, "TMEM budget");
     constexpr uint32_t kTmemCols = 512;
 
@@ -969,7 +958,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         reg_alloc<kRegsDecode>();
         const int dw = warp - kDecodeWarp0;
         const int group = dw >> 2;
-        const int set = group / kKT, gsub = group % kKT;
+        const int gsub = group % kKT;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;      // weight row inside the 128-row block
         const uint32_t lut = smem_u32(lut_tab);
@@ -1019,12 +1008,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 // Every group, with or without a k-tile, waits for the stage: it arrives on the stage's empty
                 // barrier below and must not get a ring round ahead of it.
                 ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
-                if (ok && sub < nv && ((used >> blk) & 1u))  // the MMAs of the block's previous k-tile
-                    ok = mbar_wait(bar_afree + 8 * blk, ((ph >> blk) & 1u) ^ 1u, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 if (sub < nv) {
-                    tc_fence_after();
                     const uint32_t st = stage0 + slot * stage_bytes;
                     {   // starts of the warp's 32 tiles: running sum of the tile sizes inside each median tile
                         uint32_t lo = 0u, hi = 0u, base = st + my_v;
@@ -1047,6 +1033,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                                      : "memory");
                         __syncwarp();
                     }
+                    // the MMAs of the block's previous k-tile (they ran while the tile starts were worked out)
+                    if ((used >> blk) & 1u) ok = mbar_wait(bar_afree + 8 * blk, ((ph >> blk) & 1u) ^ 1u, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
                     const uint32_t ta = tmem_a0 + blk * 32 + ((uint32_t)(quad * 32) << 16);
                     const uint32_t sp_bm = st + bm0 + (uint32_t)sub * 512;
                     uint32_t a[32];
