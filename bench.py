@@ -299,8 +299,7 @@ def main():
     status = sp.device_status()
     if rank != 0:
         if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
+            finish_ranks(dist)
         return
 
     peak, peak_kind = measured_peak_gbs()
@@ -339,8 +338,17 @@ def main():
         line["encoder"] = encoder_timing(dev)
     print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        finish_ranks(dist)
+
+
+def finish_ranks(dist):
+    """All ranks meet, then leave without tearing the communicator down: destroying a process group while a
+    captured graph still holds its collectives did not return on this stack."""
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def cublas_dense(dev, acts, order, args):
