@@ -161,6 +161,10 @@ def main():
     ap.add_argument("--case", default=None,
                     help="M,K,N[,sparsity[,split_k]]: time one SpMM shape instead of the OPT-13B set "
                          "(used for per-shape tables and for small profiler captures)")
+    ap.add_argument("--exchange", default="nccl", choices=["peer", "nccl"],
+                    help="several GPUs: how the output rows are gathered. peer = the SpMM kernel stores its rows into "
+                         "every GPU's buffer over NVLink and the next SpMM waits for the flags itself "
+                         "(spb_spmm_bitmap_v3_allgather); nccl = local SpMM, then an NCCL all-gather")
     ap.add_argument("--schedule", default="auto", choices=["auto", "static", "balanced"],
                     help="work schedule of the SpMM kernel (spb_set_schedule); auto lets the library choose per call")
     args = ap.parse_args()
@@ -213,13 +217,35 @@ def main():
     gathered = {(i, N): torch.empty((world, N, mats[i].M), dtype=torch.float16, device=dev) for (i, N) in acts} \
         if world > 1 else None
     order = [(i, N) for N in NS for i in range(len(SHAPES))]
-    launches_per_step = sum(1 + (1 if splits[k] > 1 else 0) for k in order)
+    launches_per_step = sum(1 + (1 if splits[k] > 1 and not (world > 1 and args.exchange == "peer") else 0) for k in order)
     alg_bytes_step = sum(mats[i].algorithmic_bytes(N) for (i, N) in order)
     weight_bytes = sum(2 * W.val_count + 8 * (W.M * W.K // 64) + 20 * W.G for W in mats)
+
+    # Several GPUs, peer exchange: one pair of symmetric output buffers per SpMM of the step; every SpMM waits
+    # (inside its kernel) for the exchange of the SpMM before it, as a chain of layers would, the first one of a
+    # step for the last one of the step before.
+    peer = None
+    exchange = "none"
+    if world > 1:
+        exchange = args.exchange
+        if exchange == "peer":
+            try:
+                # one buffer each: in this chain a buffer is rewritten a whole step after every rank consumed it,
+                # and a captured step then names the same buffers on every replay
+                peer = {k: spd.PeerGather(k[1], SHAPES[k[0]][0], dev, slots=1) for k in order}
+            except Exception as exc:
+                print(f"[bench] symmetric memory unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+                exchange = "nccl"
+    row_lo = {i: spd.row_shard_bounds(SHAPES[i][0], world, rank)[0] for i in range(len(SHAPES))}
+    chain = {"prev": None}
 
     def step():
         for k in order:
             i, N = k
+            if peer is not None:
+                peer[k].spmm(mats[i], acts[k], row_lo[i], after=chain["prev"])
+                chain["prev"] = peer[k]
+                continue
             sp.spmm(mats[i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
             if world > 1:
                 dist.all_gather_into_tensor(gathered[k], outs[k])
@@ -311,7 +337,7 @@ def main():
         "config": {"workload": WORKLOAD, "shapes": SHAPES, "N": NS, "sparsity": SPARSITY, "spmm_per_step": len(order),
                    "split_k": {f"{SHAPES[i][0]}x{SHAPES[i][1]}xN{N}": splits[(i, N)] for (i, N) in order},
                    "schedule": args.schedule,
-                   "parallelism": f"tp{world}_m_split_allgather" if world > 1 else "single_gpu",
+                   "parallelism": f"tp{world}_m_split_allgather_{exchange}" if world > 1 else "single_gpu",
                    "l2": f"inputs larger than L2: {weight_bytes / 1e6:.0f} MB of compressed weights per rank "
                          "rotate between reuses"},
         "hbm_gbs": achieved * world if world > 1 else achieved,

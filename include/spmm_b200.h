@@ -166,6 +166,31 @@ int spb_suggest_split_k(int M, int N, int K);
 int spb_set_schedule(int mode);
 
 /*
+ * SpMM of one row shard fused with the all-gather of the output rows (no counterpart in the reference, which
+ * is single-GPU; its caller runs an NCCL all-gather after the GEMM for the M-split of tensor parallelism).
+ * C_peers[q] is rank q's output buffer [N_Global][M_full] (fp16, column-major M_full x N like C above) as
+ * mapped into this process, q = 0..n_peers-1, this rank's own buffer included; the rows of this shard
+ * (M_shard of them, starting at row_offset) are stored into all of them.  flag_peers[q] is rank q's flag
+ * array of n_peers + 2 uint32, zero before the first use: when the launch has finished, entry `rank` of
+ * every array receives this rank's launch count.  spb_wait_flags enqueues a kernel that waits (bounded; on
+ * expiry the device status word is set) until the local array shows the next launch of every rank; work
+ * enqueued behind it sees the gathered rows.  Every rank must make the same sequence of calls on a buffer,
+ * and a buffer may be written again only after every rank has consumed it (use two buffers in turn).
+ * B_flags, when not null, is the local flag array of the exchange that produced B (a buffer gathered by an
+ * earlier call): instead of a spb_wait_flags kernel in between, this launch itself waits for that exchange,
+ * only in the warp that loads the activation tiles and with the same bound, while the weights already stream
+ * in; it counts as the one consumer of that exchange (do not also call spb_wait_flags for it).
+ * Peer memory is only ever written, never loaded from.  Needs the scratch of the calling stream (see
+ * spb_set_schedule): the first call on a stream must not be captured.
+ */
+int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compressed_A, const int* TileOffsets,
+                                 const int* TileOffsets_Median, const uint64_t* bitmap, const int* max_nnz_intile,
+                                 const uint16_t* B, uint16_t* const* C_peers, uint32_t* const* flag_peers, int n_peers,
+                                 int rank, int M_shard, int N_Global, int K_Global, int M_full, int row_offset,
+                                 uint32_t* B_flags);
+int spb_wait_flags(void* stream, uint32_t* flags, int n_peers);
+
+/*
  * Status word of the current device: 0 when no kernel of this library has hit a
  * bounded wait that ran out or an inconsistent offset since the last reset.
  * Synchronises the device.  spb_reset_device_status clears it.

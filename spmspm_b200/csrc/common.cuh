@@ -39,7 +39,18 @@ struct SpmmArgs {
     const uint16_t* B;
     uint16_t* out;  // C when split_k == 1, else the fp16 partial workspace
     int M, N, K, split_k;
+    // Fused all-gather (n_out > 0, split_k == 1): the result rows go to rows row0.. of n_out buffers
+    // [N][ld_out] (this GPU's and its peers'), then entry flag_index of n_flags flag arrays gets the
+    // launch's sequence number (the incremented value of *sequence).
+    uint16_t* outs[8] = {};
+    uint32_t* flags[8] = {};
+    int n_out = 0, ld_out = 0, row0 = 0, n_flags = 0, flag_index = 0;
+    uint32_t* sequence = nullptr;
+    // flag array (on this GPU) of the exchange that produced B, or null; wait_n ranks
+    uint32_t* wait_flags = nullptr;
+    int wait_n = 0;
 };
+cudaError_t wait_flags_launch(cudaStream_t s, uint32_t* flags, int n, int* status);
 cudaError_t spmm_launch(cudaStream_t s, const SpmmArgs& a);
 int suggest_split_k(int M, int N, int K);
 // Work schedule of the SpMM kernel: 1 = static (one work item per split-K range, no scratch), 2 = balanced

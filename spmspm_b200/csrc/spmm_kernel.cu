@@ -65,6 +65,7 @@ static_assert(128 * kRegsControl + 128 * kRegsEpilogue + 128 * kDecodeGroups * k
               "register budget: the resized roles must fit into the CTA's launch allocation");
 static_assert(kRegsControl <= kRegsLaunch && kRegsEpilogue <= kRegsLaunch && kRegsDecode >= kRegsLaunch,
               "roles that shrink must not exceed, roles that grow must not undercut the launch allocation");
+constexpr int kMaxPeers = 8;
 constexpr int kMaxStages = 24;
 constexpr int kHeaderBytes = 3072;  // barriers and flags (1 KB), then 128 bytes of tile starts per decode warp
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -86,6 +87,20 @@ struct KernelParams {
     float* partials;
     int* counters;
     int balanced, units;
+    // Output: normally one buffer [N][M] (or the split-K partials).  For the fused all-gather the rows of this
+    // launch go to rows row0.. of n_out buffers [N][ld_out], this GPU's and its peers' (peer memory mapped
+    // into this process), and when the last CTA has finished, the launch's sequence number is written to
+    // entry flag_index of every peer's flag array.
+    uint16_t* outs[kMaxPeers];
+    uint32_t* flags[kMaxPeers];
+    int n_out, ld_out, row0, n_flags, flag_index;
+    uint32_t* sequence;  // this GPU's count of fused launches on these buffers
+    int* done;           // CTAs of the launch that have finished
+    // The activations of this launch are the result of an earlier exchange: its flag array on this GPU
+    // ([wait_n] ranks' sequence numbers, then this GPU's own launch count, then the number of exchanges
+    // consumed so far).  The warp that loads the activation tiles polls it, everything else starts at once.
+    uint32_t* wait_flags;
+    int wait_n;
 };
 
 // ------------------------------------------------------------------ PTX helpers
@@ -660,6 +675,25 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             load_batch(cur);
             Batch nxt = batch_after(cur);
             load_batch(nxt);
+            if (prole == 2 && p.wait_flags && st.valid) {
+                // the activations come out of an exchange between the GPUs: bounded wait for every rank's rows
+                const uint32_t want = *reinterpret_cast<volatile uint32_t*>(p.wait_flags + p.wait_n + 1) + 1u;
+                bool here = lane >= p.wait_n;
+                for (uint32_t i = 0; i < kSpinLimit && !here; ++i) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + lane) : "memory");
+                    here = (int32_t)(v - want) >= 0;
+                    if (!here) {
+                        if (*abort_flag) break;
+                        __nanosleep(100);
+                    }
+                }
+                if (!here) *abort_flag = 1;
+                ok = __all_sync(0xffffffffu, here);
+                // the rows were written through the generic proxy by other GPUs, the tile loads below read them
+                // through the async proxy
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+            }
             while (st.valid && ok) {
                 const Item cw = st.w;
                 const int ckk0 = kk0;
@@ -794,11 +828,16 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         const bool leader = warp == kEpilogueWarp0 && lane == 0;
         while (ok && wk.next(p, w)) {
             const int grow = w.y * 128 + row_in_block;
-            uint16_t* out = p.out + (p.split_k > 1 ? (size_t)w.batch * p.M * p.N : (size_t)0);
+            // element (col, grow) of this launch's result, in every output buffer
+            const size_t out0 = (p.split_k > 1 ? (size_t)w.batch * p.M * p.N : (size_t)0) + (size_t)p.row0 + (size_t)grow;
+            auto store = [&](int col, uint16_t v) {
+                const size_t at = out0 + (size_t)col * p.ld_out;
+                for (int q = 0; q < p.n_out; ++q) p.outs[q][at] = v;
+            };
             if (w.nk == 0) {
                 for (int n = 0; n < NPAD; ++n) {
                     const int col = w.nt * NPAD + n;
-                    if (col < p.N && grow < p.M) out[(size_t)col * p.M + grow] = 0;
+                    if (col < p.N && grow < p.M) store(col, (uint16_t)0);
                 }
                 continue;
             }
@@ -882,8 +921,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
 #pragma unroll
                 for (int n = 0; n < 16; ++n) {
                     const int col = w.nt * NPAD + c * 16 + n;
-                    if (col < p.N && grow < p.M)
-                        out[(size_t)col * p.M + grow] = __half_as_ushort(__float2half_rn(acc[n]));
+                    if (col < p.N && grow < p.M) store(col, __half_as_ushort(__float2half_rn(acc[n])));
                 }
             };
 #pragma unroll
@@ -947,6 +985,20 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 }
             }
             ++idx;
+        }
+        if (p.n_flags > 0) {
+            // Fused all-gather: every thread's stores to the peers are made visible system-wide before the CTA
+            // counts itself as finished; the CTA that completes the count numbers the launch and tells the peers.
+            __threadfence_system();
+            bar_sync_epilogue();
+            if (leader && atomicAdd(p.done, 1) == (int)gridDim.x - 1) {
+                *p.done = 0;
+                __threadfence_system();
+                const uint32_t seq = atomicAdd(p.sequence, 1u) + 1u;
+                for (int q = 0; q < p.n_flags; ++q)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[q] + p.flag_index), "r"(seq) : "memory");
+                if (p.wait_flags) p.wait_flags[p.wait_n + 1] += 1u;  // every CTA of this launch has read it
+            }
         }
     } else {
         // ================================================================= decode
@@ -1170,8 +1222,8 @@ const ScratchSet* scratch_for(cudaStream_t st, int dev, int sms, bool may_create
             cudaGetLastError();
             return nullptr;
         }
-        if (cudaMalloc(&n.counters, (size_t)kCounterCap * sizeof(int)) != cudaSuccess ||
-            cudaMemset(n.counters, 0, (size_t)kCounterCap * sizeof(int)) != cudaSuccess ||
+        if (cudaMalloc(&n.counters, (size_t)(kCounterCap + 16) * sizeof(int)) != cudaSuccess ||
+            cudaMemset(n.counters, 0, (size_t)(kCounterCap + 16) * sizeof(int)) != cudaSuccess ||
             cudaDeviceSynchronize() != cudaSuccess) {
             cudaGetLastError();
             cudaFree(n.partials);
@@ -1277,6 +1329,21 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     p.counters = nullptr;
     p.balanced = 0;
     p.units = 0;
+    const bool fused = a.n_out > 0;
+    for (int q = 0; q < kMaxPeers; ++q) {
+        p.outs[q] = fused && q < a.n_out ? a.outs[q] : nullptr;
+        p.flags[q] = fused && q < a.n_flags ? a.flags[q] : nullptr;
+    }
+    if (!fused) p.outs[0] = a.out;
+    p.n_out = fused ? a.n_out : 1;
+    p.ld_out = fused ? a.ld_out : a.M;
+    p.row0 = fused ? a.row0 : 0;
+    p.n_flags = fused ? a.n_flags : 0;
+    p.flag_index = a.flag_index;
+    p.sequence = a.sequence;
+    p.done = nullptr;
+    p.wait_flags = fused ? a.wait_flags : nullptr;
+    p.wait_n = a.wait_n;
     const int mode = g_schedule.load();
     if (mode != 1 && t_static_depth == 0 && (units + 1) * di.sms < (1LL << 31) && p.num_items <= kCounterCap &&
         no_empty_range && (mode == 2 || prefer_balanced(p.row_blocks, p.n_tiles, p.kt_total, a.split_k, di.sms, NPAD))) {
@@ -1288,6 +1355,16 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
             p.balanced = 1;
             p.units = (int)units;
         }
+    }
+    if (p.n_flags > 0) {
+        // the count of finished CTAs lives behind the arrival counters of the stream's scratch
+        const ScratchSet* sc = scratch_for(s, dev, di.sms, !stream_is_capturing(s));
+        if (!sc) {
+            set_error("fused all-gather: no scratch for this stream (more than %d streams in use, or the first call "
+                      "on the stream is being captured)", kScratchSets);
+            return cudaErrorNotReady;
+        }
+        p.done = sc->counters + kCounterCap;
     }
 
     static bool attr_set[64] = {false};
@@ -1333,7 +1410,7 @@ cudaError_t reset_schedule_scratch()
     std::lock_guard<std::mutex> lock(g_scratch_mu);
     for (int i = 0; i < kScratchSets; ++i) {
         if (!g_scratch[dev][i].taken) continue;
-        e = cudaMemset(g_scratch[dev][i].counters, 0, (size_t)kCounterCap * sizeof(int));
+        e = cudaMemset(g_scratch[dev][i].counters, 0, (size_t)(kCounterCap + 16) * sizeof(int));
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;

@@ -55,3 +55,67 @@ def spmm_m_sharded(W_local, B, compute, group=None, **kw):
 def spmm_k_sharded(W_local, B_local, compute, group=None, **kw):
     """out-proj / FC2 style: W_local holds this rank's columns, B_local the matching slice of the activations."""
     return all_reduce_partial(compute(W_local, B_local, **kw), group)
+
+
+class PeerGather:
+    """Output buffers for the SpMM fused with the all-gather of its output rows (spb_spmm_bitmap_v3_allgather).
+
+    Every rank allocates `slots` output buffers [N, M_full] and a flag array per buffer in symmetric memory
+    (torch.distributed._symmetric_memory: the peers' copies are mapped into this process).  `spmm(W_local, B)`
+    makes this rank's SpMM store its rows into every rank's current buffer; `wait()` enqueues the bounded wait for
+    all ranks' rows and returns the gathered [N, M_full] tensor of this rank.  Calls alternate between the
+    buffers, so a buffer is rewritten only after `slots - 1` further exchanges; every rank must make the same
+    sequence of calls.
+    """
+
+    def __init__(self, N, M_full, device, group=None, slots=2):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("PeerGather serves up to 8 ranks")
+        self.N, self.M_full = N, M_full
+        self.bufs, self.flags, self._cptrs, self._fptrs = [], [], [], []
+        for _ in range(slots):
+            buf = symm_mem.empty((N, M_full), dtype=torch.float16, device=device)
+            flg = symm_mem.empty((self.world + 2,), dtype=torch.int32, device=device)
+            buf.zero_()
+            flg.zero_()
+            hb = symm_mem.rendezvous(buf, self.group.group_name)
+            hf = symm_mem.rendezvous(flg, self.group.group_name)
+            self.bufs.append(buf)
+            self.flags.append(flg)
+            self._cptrs.append((ctypes.c_void_p * self.world)(*[int(p) for p in hb.buffer_ptrs]))
+            self._fptrs.append((ctypes.c_void_p * self.world)(*[int(p) for p in hf.buffer_ptrs]))
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)   # every rank's buffers and flags are zero before anybody writes
+        self._turn = 0
+
+    def spmm(self, W_local, B, row_offset, after=None, stream=None):
+        """Enqueue this rank's SpMM; its rows [row_offset, row_offset + W_local.M) go to every rank's buffer.
+
+        `after`: a PeerGather whose current exchange produced B (its `gathered()` buffer): the kernel itself waits
+        for that exchange before it reads B, and that exchange counts as consumed."""
+        from . import api
+        flags = None
+        if after is not None:   # before this call's own buffer is chosen: `after` may be this object
+            flags = after.flags[after._turn % len(after.bufs)]
+            after._turn += 1
+        slot = self._turn % len(self.bufs)
+        api.spmm_allgather(W_local, B, self._cptrs[slot], self._fptrs[slot], self.world, self.rank, self.M_full,
+                           row_offset, B_flags=flags, stream=stream)
+        return slot
+
+    def gathered(self):
+        """This rank's buffer of the current exchange (complete only after `wait()` or a consuming `spmm(after=)`)."""
+        return self.bufs[self._turn % len(self.bufs)]
+
+    def wait(self, stream=None):
+        """Enqueue the wait for all ranks' rows of the current exchange; returns this rank's gathered tensor."""
+        from . import api
+        slot = self._turn % len(self.bufs)
+        api.wait_flags(self.flags[slot], self.world, stream=stream)
+        self._turn += 1
+        return self.bufs[slot]
