@@ -217,7 +217,7 @@ def main():
     gathered = {(i, N): torch.empty((world, N, mats[i].M), dtype=torch.float16, device=dev) for (i, N) in acts} \
         if world > 1 else None
     order = [(i, N) for N in NS for i in range(len(SHAPES))]
-    launches_per_step = sum(1 + (1 if splits[k] > 1 and not (world > 1 and args.exchange == "peer") else 0) for k in order)
+    launches_per_step = sum(1 + (1 if splits[k] > 1 else 0) for k in order)
     alg_bytes_step = sum(mats[i].algorithmic_bytes(N) for (i, N) in order)
     weight_bytes = sum(2 * W.val_count + 8 * (W.M * W.K // 64) + 20 * W.G for W in mats)
 
@@ -243,7 +243,7 @@ def main():
         for k in order:
             i, N = k
             if peer is not None:
-                peer[k].spmm(mats[i], acts[k], row_lo[i], after=chain["prev"])
+                peer[k].spmm(mats[i], acts[k], row_lo[i], after=chain["prev"], split_k=splits[k], workspace=ws)
                 chain["prev"] = peer[k]
                 continue
             sp.spmm(mats[i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)

@@ -180,6 +180,8 @@ int spb_set_schedule(int mode);
  * earlier call): instead of a spb_wait_flags kernel in between, this launch itself waits for that exchange,
  * only in the warp that loads the activation tiles and with the same bound, while the weights already stream
  * in; it counts as the one consumer of that exchange (do not also call spb_wait_flags for it).
+ * With Split_K > 1 the fp16 partial sums go to Reduction_Workspace (Split_K*M_shard*N_Global halves) as in
+ * spb_spmm_bitmap_v3 and the reduction kernel does the stores to the peers and the flags.
  * Peer memory is only ever written, never loaded from.  Needs the scratch of the calling stream (see
  * spb_set_schedule): the first call on a stream must not be captured.
  */
@@ -187,7 +189,7 @@ int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compressed_A, con
                                  const int* TileOffsets_Median, const uint64_t* bitmap, const int* max_nnz_intile,
                                  const uint16_t* B, uint16_t* const* C_peers, uint32_t* const* flag_peers, int n_peers,
                                  int rank, int M_shard, int N_Global, int K_Global, int M_full, int row_offset,
-                                 uint32_t* B_flags);
+                                 uint32_t* B_flags, uint16_t* Reduction_Workspace, int Split_K);
 int spb_wait_flags(void* stream, uint32_t* flags, int n_peers);
 
 /*

@@ -249,18 +249,20 @@ def spmm_noalloc(W: BitmapMatrix, B, split_k, out, stream=None):
 
 
 def spmm_allgather(W: BitmapMatrix, B, C_peers, flag_peers, n_peers, rank, M_full, row_offset, B_flags=None,
-                   stream=None):
+                   split_k=1, workspace=None, stream=None):
     """spb_spmm_bitmap_v3_allgather: SpMM of a row shard whose output rows are stored into every rank's buffer.
 
     C_peers / flag_peers are ctypes arrays of n_peers device pointers (see spmspm_b200.dist.PeerGather); B_flags is
     the local flag tensor of the exchange that produced B, if B is a gathered buffer not yet waited for."""
     if not (B.is_cuda and B.dtype == torch.float16 and B.dim() == 2 and B.is_contiguous() and B.shape[1] == W.K):
         raise SpmmError("B must be a contiguous CUDA float16 [N,K] tensor")
+    if split_k > 1 and workspace is None:
+        workspace = torch.empty(split_k * B.shape[0] * W.M, dtype=torch.float16, device=B.device)
     with torch.cuda.device(B.device):
         code = _lib.load().spb_spmm_bitmap_v3_allgather(_stream_ptr(stream), _ptr(W.vals), _ptr(W.gtile), _ptr(W.mtile),
                                                         _ptr(W.bitmap), _ptr(W.max_nnz), _ptr(B), C_peers, flag_peers,
                                                         n_peers, rank, W.M, B.shape[0], W.K, M_full, row_offset,
-                                                        _ptr(B_flags))
+                                                        _ptr(B_flags), _ptr(workspace), split_k)
     _check(code, "spb_spmm_bitmap_v3_allgather")
 
 

@@ -51,6 +51,7 @@ struct SpmmArgs {
     int wait_n = 0;
 };
 cudaError_t wait_flags_launch(cudaStream_t s, uint32_t* flags, int n, int* status);
+cudaError_t exchange_counter(cudaStream_t s, int** out);  // a zeroed int of the stream's scratch, for CTA counting
 cudaError_t spmm_launch(cudaStream_t s, const SpmmArgs& a);
 int suggest_split_k(int M, int N, int K);
 // Work schedule of the SpMM kernel: 1 = static (one work item per split-K range, no scratch), 2 = balanced

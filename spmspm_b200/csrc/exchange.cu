@@ -6,6 +6,7 @@
 // until its own flag array shows the current sequence number from every rank.  No load ever touches peer memory.
 #include "../../include/spmm_b200.h"
 #include "common.cuh"
+#include <cuda_fp16.h>
 
 namespace spb {
 namespace {
@@ -36,6 +37,57 @@ __global__ void wait_flags_kernel(uint32_t* flags, int n, int* status)
     if (!ok) atomicOr(status, (int)kStatusWaitTimeout);
 }
 
+// Split-K reduction (the arithmetic of reduction.cu: fp32 sum of the fp16 partials in range order, one fp16
+// rounding) whose result rows go to rows row0.. of every GPU's [N][ld] buffer; the last block numbers the
+// exchange and writes the flags, like the SpMM kernel does when it gathers directly.
+struct GatherOut {
+    uint16_t* outs[8];
+    uint32_t* flags[8];
+    int n, flag_index;
+    uint32_t* sequence;
+    int* done;
+};
+__global__ void __launch_bounds__(256)
+splitk_reduce_gather_kernel(const GatherOut g, const uint16_t* __restrict__ W, int M, size_t mn, int split_k, int ld,
+                            int row0)
+{
+    const size_t e = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (e < mn) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int s = 0; s < split_k; ++s) {
+            const uint4 v = *reinterpret_cast<const uint4*>(W + (size_t)s * mn + e);
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+            }
+        }
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+        const size_t col = e / (size_t)M, row = e - col * (size_t)M;  // 8 consecutive rows of one column
+        const size_t at = col * (size_t)ld + (size_t)row0 + row;
+        for (int q = 0; q < g.n; ++q) *reinterpret_cast<uint4*>(g.outs[q] + at) = o;
+    }
+    // one system-scope fence per block, behind the barrier that orders the other threads' stores before it
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(g.sequence) + 1u;  // exchanges on a buffer are stream-ordered
+    __threadfence_system();
+    if (atomicAdd(g.done, 1) == (int)gridDim.x - 1) {
+        *g.done = 0;
+        __threadfence();
+        *g.sequence = seq;
+        for (int q = 0; q < g.n; ++q)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(g.flags[q] + g.flag_index), "r"(seq) : "memory");
+    }
+}
+
 }  // namespace
 
 cudaError_t wait_flags_launch(cudaStream_t s, uint32_t* flags, int n, int* status)
@@ -51,7 +103,7 @@ extern "C" int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compre
                                             const int* max_nnz_intile, const uint16_t* B, uint16_t* const* C_peers,
                                             uint32_t* const* flag_peers, int n_peers, int rank, int M_shard,
                                             int N_Global, int K_Global, int M_full, int row_offset,
-                                            uint32_t* B_flags)
+                                            uint32_t* B_flags, uint16_t* Reduction_Workspace, int Split_K)
 {
     if (n_peers < 1 || n_peers > 8 || rank < 0 || rank >= n_peers || !C_peers || !flag_peers) {
         spb::set_error("spb_spmm_bitmap_v3_allgather: 1..8 peers, rank inside, pointer tables required");
@@ -79,7 +131,41 @@ extern "C" int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compre
     a.M = M_shard;
     a.N = N_Global;
     a.K = K_Global;
-    a.split_k = 1;
+    if (Split_K < 1 || Split_K > K_Global / 64 || (Split_K > 1 && (!Reduction_Workspace ||
+                                                                  (reinterpret_cast<uintptr_t>(Reduction_Workspace) & 15u)))) {
+        spb::set_error("spb_spmm_bitmap_v3_allgather: Split_K=%d needs 1..%d and, above 1, an aligned workspace", Split_K,
+                       K_Global / 64);
+        return (int)cudaErrorInvalidValue;
+    }
+    a.split_k = Split_K;
+    a.wait_flags = B_flags;
+    a.wait_n = n_peers;
+    if (Split_K > 1) {
+        // fp16 partials into the workspace as usual (the SpMM kernel still waits for B's exchange); the
+        // reduction then stores the rows into the peers' buffers and writes the flags
+        spb::GatherOut g;
+        for (int q = 0; q < 8; ++q) {
+            g.outs[q] = q < n_peers ? C_peers[q] : nullptr;
+            g.flags[q] = q < n_peers ? flag_peers[q] : nullptr;
+            if (q < n_peers && (!C_peers[q] || !flag_peers[q] || (reinterpret_cast<uintptr_t>(C_peers[q]) & 15u))) {
+                spb::set_error("spb_spmm_bitmap_v3_allgather: peer %d: null or misaligned buffer", q);
+                return (int)cudaErrorInvalidValue;
+            }
+        }
+        g.n = n_peers;
+        g.flag_index = rank;
+        g.sequence = flag_peers[rank] + n_peers;
+        cudaError_t e = spb::exchange_counter((cudaStream_t)stream, &g.done);
+        if (e != cudaSuccess) return (int)e;
+        a.out = Reduction_Workspace;
+        e = spb::spmm_launch((cudaStream_t)stream, a);
+        if (e != cudaSuccess) return (int)e;
+        const size_t mn = (size_t)M_shard * N_Global;
+        const unsigned blocks = (unsigned)((mn / 8 + 255) / 256);
+        spb::splitk_reduce_gather_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(g, Reduction_Workspace, M_shard, mn,
+                                                                                 Split_K, M_full, row_offset);
+        return (int)cudaGetLastError();
+    }
     for (int q = 0; q < n_peers; ++q) {
         if (!C_peers[q] || !flag_peers[q] || (reinterpret_cast<uintptr_t>(C_peers[q]) & 15u)) {
             spb::set_error("spb_spmm_bitmap_v3_allgather: peer %d: null or misaligned buffer", q);
@@ -94,8 +180,6 @@ extern "C" int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compre
     a.row0 = row_offset;
     a.flag_index = rank;
     a.sequence = flag_peers[rank] + n_peers;  // this rank's own array is local memory
-    a.wait_flags = B_flags;
-    a.wait_n = n_peers;
     return (int)spb::spmm_launch((cudaStream_t)stream, a);
 }
 

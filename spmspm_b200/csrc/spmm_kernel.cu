@@ -677,10 +677,14 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             load_batch(nxt);
             if (prole == 2 && p.wait_flags && st.valid) {
                 // the activations come out of an exchange between the GPUs: bounded wait for every rank's rows
-                const uint32_t want = *reinterpret_cast<volatile uint32_t*>(p.wait_flags + p.wait_n + 1) + 1u;
                 bool here = lane >= p.wait_n;
+                // the count of consumed exchanges and the first look at the flags travel together (the plain
+                // load first: nothing may pass an acquire load that is still under way)
+                const uint32_t want = *reinterpret_cast<volatile uint32_t*>(p.wait_flags + p.wait_n + 1) + 1u;
+                uint32_t v = 0;
+                if (!here) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + lane) : "memory");
+                here = here || (int32_t)(v - want) >= 0;
                 for (uint32_t i = 0; i < kSpinLimit && !here; ++i) {
-                    uint32_t v;
                     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + lane) : "memory");
                     here = (int32_t)(v - want) >= 0;
                     if (!here) {
@@ -826,6 +830,14 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         wk.init(p);
         Item w;
         const bool leader = warp == kEpilogueWarp0 && lane == 0;
+        // Fused exchange: this launch's number and the count of consumed exchanges are read now, long before
+        // they are needed (launches on one set of buffers are ordered by the stream, so nobody changes them
+        // in between), so that the end of the kernel is a chain of stores without loads.
+        uint32_t my_seq = 0, consumed = 0;
+        if (leader && p.done) {
+            if (p.n_flags > 0) my_seq = *reinterpret_cast<volatile uint32_t*>(p.sequence) + 1u;
+            if (p.wait_flags) consumed = *reinterpret_cast<volatile uint32_t*>(p.wait_flags + p.wait_n + 1) + 1u;
+        }
         while (ok && wk.next(p, w)) {
             const int grow = w.y * 128 + row_in_block;
             // element (col, grow) of this launch's result, in every output buffer
@@ -986,18 +998,23 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             }
             ++idx;
         }
-        if (p.n_flags > 0) {
+        if (p.done) {
             // Fused all-gather: every thread's stores to the peers are made visible system-wide before the CTA
             // counts itself as finished; the CTA that completes the count numbers the launch and tells the peers.
-            __threadfence_system();
+            // (the barrier orders the other threads' stores before the leader's system-scope fence, which is
+            // cumulative: one fence per CTA instead of one per thread)
             bar_sync_epilogue();
+            if (leader && p.n_flags > 0) __threadfence_system();
             if (leader && atomicAdd(p.done, 1) == (int)gridDim.x - 1) {
                 *p.done = 0;
-                __threadfence_system();
-                const uint32_t seq = atomicAdd(p.sequence, 1u) + 1u;
-                for (int q = 0; q < p.n_flags; ++q)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[q] + p.flag_index), "r"(seq) : "memory");
-                if (p.wait_flags) p.wait_flags[p.wait_n + 1] += 1u;  // every CTA of this launch has read it
+                if (p.n_flags > 0) {
+                    __threadfence();  // the other CTAs' counts (each behind its own system-scope fence) were seen
+                    *p.sequence = my_seq;
+                    for (int q = 0; q < p.n_flags; ++q)
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[q] + p.flag_index), "r"(my_seq)
+                                     : "memory");
+                }
+                if (p.wait_flags) p.wait_flags[p.wait_n + 1] = consumed;  // every CTA of this launch has read it
             }
         }
     } else {
@@ -1342,7 +1359,7 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     p.flag_index = a.flag_index;
     p.sequence = a.sequence;
     p.done = nullptr;
-    p.wait_flags = fused ? a.wait_flags : nullptr;
+    p.wait_flags = a.wait_flags;
     p.wait_n = a.wait_n;
     const int mode = g_schedule.load();
     if (mode != 1 && t_static_depth == 0 && (units + 1) * di.sms < (1LL << 31) && p.num_items <= kCounterCap &&
@@ -1356,7 +1373,7 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
             p.units = (int)units;
         }
     }
-    if (p.n_flags > 0) {
+    if (p.n_flags > 0 || p.wait_flags) {
         // the count of finished CTAs lives behind the arrival counters of the stream's scratch
         const ScratchSet* sc = scratch_for(s, dev, di.sms, !stream_is_capturing(s));
         if (!sc) {
@@ -1392,6 +1409,21 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
 }
 
 }  // namespace
+
+cudaError_t exchange_counter(cudaStream_t s, int** out)
+{
+    DeviceInfo di = device_info();
+    int dev = 0;
+    if (!di.ok || cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
+    const ScratchSet* sc = scratch_for(s, dev, di.sms, !stream_is_capturing(s));
+    if (!sc) {
+        set_error("fused all-gather: no scratch for this stream (more than %d streams in use, or the first call on "
+                  "the stream is being captured)", kScratchSets);
+        return cudaErrorNotReady;
+    }
+    *out = sc->counters + kCounterCap + 1;
+    return cudaSuccess;
+}
 
 int set_schedule(int mode)
 {

@@ -93,7 +93,7 @@ class PeerGather:
         dist.barrier(self.group)   # every rank's buffers and flags are zero before anybody writes
         self._turn = 0
 
-    def spmm(self, W_local, B, row_offset, after=None, stream=None):
+    def spmm(self, W_local, B, row_offset, after=None, split_k=1, workspace=None, stream=None):
         """Enqueue this rank's SpMM; its rows [row_offset, row_offset + W_local.M) go to every rank's buffer.
 
         `after`: a PeerGather whose current exchange produced B (its `gathered()` buffer): the kernel itself waits
@@ -105,7 +105,7 @@ class PeerGather:
             after._turn += 1
         slot = self._turn % len(self.bufs)
         api.spmm_allgather(W_local, B, self._cptrs[slot], self._fptrs[slot], self.world, self.rank, self.M_full,
-                           row_offset, B_flags=flags, stream=stream)
+                           row_offset, B_flags=flags, split_k=split_k, workspace=workspace, stream=stream)
         return slot
 
     def gathered(self):

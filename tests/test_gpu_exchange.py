@@ -40,14 +40,21 @@ def test_single_rank_exchange_and_chained_wait(lib_built):
     sp.spmm_allgather(W, Bd, cptr[0], fptr[0], 1, 0, M_full, lo, B_flags=flags[1])
     sp.wait_flags(flags[0], 1)
     torch.cuda.synchronize()
+    first = bufs[0].clone()
+    # the same with Split_K = 3: the reduction kernel stores the rows and writes the flag
+    sp.spmm_allgather(W, Bd, cptr[1], fptr[1], 1, 0, M_full, lo, split_k=3)
+    sp.spmm_allgather(W, Bd, cptr[0], fptr[0], 1, 0, M_full, lo, B_flags=flags[1], split_k=3)
+    sp.wait_flags(flags[0], 1)
+    torch.cuda.synchronize()
+    assert float((bufs[0].float() - first.float()).abs().max()) <= 4e-3 * float(first.float().abs().max())
     for b in bufs:
         out = b.cpu().numpy().astype(np.float32)
         got = out[:, lo:lo + 512]
         assert np.abs(got - ref).max() <= 1e-2 * np.abs(ref).max()
         assert np.all(out[:, :lo] == 7.0) and np.all(out[:, lo + 512:] == 7.0)   # only the shard's rows were written
     f0, f1 = flags[0].cpu().tolist(), flags[1].cpu().tolist()
-    assert f0 == [2, 2, 2]      # two launches numbered 1, 2; two exchanges consumed
-    assert f1 == [1, 1, 1]      # one launch, consumed by the chained launch
+    assert f0 == [3, 3, 3]      # three launches numbered 1..3; three exchanges consumed
+    assert f1 == [2, 2, 2]      # two launches, each consumed by the chained launch after it
     assert sp.device_status() == 0
 
 
@@ -84,13 +91,17 @@ W = sp.encode_device(torch.from_numpy(A[lo:hi].copy()).to(dev))
 ref = sp.spmm(sp.encode_device(torch.from_numpy(A).to(dev)), B, split_k=1).float()
 pg = spd.PeerGather(N, M, dev)
 bad = 0
-for it in range(4):                      # wait kernel, then the chained form
-    pg.spmm(W, B, lo, after=pg if it >= 2 else None)
-    if it < 2 or it == 3:
-        out = pg.wait()
-        torch.cuda.synchronize()
-        bad += int(float((out.float() - ref).abs().max()) > 2e-3 * float(ref.abs().max()))
-    dist.barrier()
+def check(out):
+    torch.cuda.synchronize()
+    return int(float((out.float() - ref).abs().max()) > 2e-3 * float(ref.abs().max()))
+pg.spmm(W, B, lo)                               # consumed by a wait kernel
+bad += check(pg.wait())
+dist.barrier()
+pg.spmm(W, B, lo, split_k=2)                    # a chain: each launch waits for the exchange before it
+pg.spmm(W, B, lo, after=pg)
+pg.spmm(W, B, lo, after=pg, split_k=2)
+bad += check(pg.wait())
+dist.barrier()
 bad += int(sp.device_status() != 0)
 print("RESULT", rank, bad, flush=True)
 dist.barrier(); os._exit(0 if bad == 0 else 1)
