@@ -607,11 +607,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     // and afree (the MMAs that read it have completed), so that a decode group only ever waits for the
     // tensor core's work on its own k-tiles, never for another group.  Which phase of a block's barriers
     // comes next is kept as one bit per block (ph) by everybody who walks the stage sequence.
-    if (S < 1) {
-        // A single stage does not fit (cannot happen with the launch configuration used by the host
-        // code); leave cleanly.
-        if (threadIdx.x == 0) atomicOr(p.status, (int)kStatusBadOffsets);
-    } else if (warp < kEpilogueWarp0) {
+    // (Nothing above this line needs the stage size, which depends on max_nnz_intile, a load from global
+    // memory: the producers below start fetching the tile offsets before they look at it.)
+    if (warp < kEpilogueWarp0) {
         reg_dealloc<kRegsControl>();
         if (warp != kMmaWarp) {
             // ================================================================= producers
@@ -675,7 +673,14 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             load_batch(cur);
             Batch nxt = batch_after(cur);
             load_batch(nxt);
-            if (prole == 2 && p.wait_flags && st.valid) {
+            if (S < 1) {
+                // A single stage does not fit (cannot happen with the launch configuration used by the host
+                // code): nothing is copied, the other warps give up on their bounded waits.
+                if (lane == 0 && prole == 0) atomicOr(p.status, (int)kStatusBadOffsets);
+                *abort_flag = 1;
+                ok = false;
+            }
+            if (ok && prole == 2 && p.wait_flags && st.valid) {
                 // the activations come out of an exchange between the GPUs: bounded wait for every rank's rows
                 bool here = lane >= p.wait_n;
                 // the count of consumed exchanges and the first look at the flags travel together (the plain
@@ -929,11 +934,21 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     }
                 }
             };
+            // 16 columns of the result to every output buffer: the loop over the buffers is the outer one so
+            // that the 16 stores to a buffer are issued back to back (the end of the kernel waits for them)
             auto write_out = [&](const float* acc, int c) {
+                uint16_t h[16];
 #pragma unroll
-                for (int n = 0; n < 16; ++n) {
-                    const int col = w.nt * NPAD + c * 16 + n;
-                    if (col < p.N && grow < p.M) store(col, __half_as_ushort(__float2half_rn(acc[n])));
+                for (int n = 0; n < 16; ++n) h[n] = __half_as_ushort(__float2half_rn(acc[n]));
+                const int col0 = w.nt * NPAD + c * 16;
+                if (grow < p.M) {
+#pragma unroll 1
+                    for (int q = 0; q < p.n_out; ++q) {
+                        uint16_t* o = p.outs[q] + out0 + (size_t)col0 * p.ld_out;
+#pragma unroll
+                        for (int n = 0; n < 16; ++n)
+                            if (col0 + n < p.N) o[(size_t)n * p.ld_out] = h[n];
+                    }
                 }
             };
 #pragma unroll
@@ -1055,14 +1070,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         // k-tiles (the end of a work item) then costs no more than the k-tiles it has.
         uint32_t slot = 0, round = 0, rot = 0, abuf = 0, ph = 0, used = 0;
         const uint32_t tsel = tile_tab + tile_sel;
-#ifndef SPB_STAGGER_NS
-#define SPB_STAGGER_NS 450
-#endif
-        // The start of a k-tile (barrier checks, tile starts) is a chain of dependent instructions, its body
-        // is bound by arithmetic throughput.  Groups that start together stay together, all waiting and then
-        // all computing; started a quarter of a k-tile's time apart, one group's waiting overlaps the others'
-        // arithmetic on every scheduler, and nothing in the protocol pulls them back together.
-        if (gsub > 0) __nanosleep((unsigned)(SPB_STAGGER_NS * gsub));
+        // The start of a k-tile (barrier checks, tile starts) is a chain of dependent instructions, its body is
+        // bound by arithmetic throughput.  Because no group ever waits for another one (see the A block
+        // barriers), the groups drift apart after the first k-tiles, and one group's chains then overlap the
+        // others' arithmetic on every scheduler; starting them apart on purpose measured the same.
         bool ok = true;
         Walk wk;
         wk.init(p);
