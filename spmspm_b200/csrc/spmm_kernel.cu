@@ -316,11 +316,12 @@ struct Walk {
         r0 = row * p.kt_total + ks;
         r1 = row * p.kt_total + ke;
     }
+    template <bool kBalanced>
     __device__ __forceinline__ void init(const KernelParams& p)
     {
         pos = -1;
         phase = 0;
-        if (!p.balanced) {
+        if (!kBalanced) {
             begin = blockIdx.x;
             end = p.num_items;
             lo_end = hi_beg = order = 0;
@@ -349,9 +350,10 @@ struct Walk {
         else if (hi)
             order = 1 | 2 << 2 | 3 << 4;
     }
+    template <bool kBalanced>
     __device__ __forceinline__ bool next(const KernelParams& p, Item& it)
     {
-        if (!p.balanced) {
+        if (!kBalanced) {
             if (begin >= end) return false;
             const int per_nt = p.row_blocks * p.split_k;
             it.nt = begin / per_nt;
@@ -509,7 +511,12 @@ __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
     o[3] = prmt(t1, 0u, u.h);
 }
 
-template <int NPAD>
+// kExchange: the variant used by the fused all-gather (several output buffers, completion flags, activations
+// that come out of an earlier exchange).  The plain variant carries none of that code: the decode loop is
+// sensitive to the size of the kernel around it (the same source with the exchange code compiled in ran 5 %
+// slower on calls that never used it).  kBalanced: the work schedule (see Walk); the static variant carries
+// no code for the exchange of partial sums.
+template <int NPAD, bool kExchange, bool kBalanced>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtensorMap tmap_b)
 {
@@ -632,7 +639,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             };
             auto advance = [&](Cursor& c) {
                 do {
-                    c.valid = c.wk.next(p, c.w);
+                    c.valid = c.wk.template next<kBalanced>(p, c.w);
                 } while (c.valid && c.w.nk == 0);
                 ++c.seq;
             };
@@ -664,7 +671,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             bool ok = true;
             int kk0 = 0;
             Cursor st;
-            st.wk.init(p);
+            st.wk.template init<kBalanced>(p);
             st.seq = -1;
             advance(st);
             Batch cur;
@@ -680,7 +687,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 *abort_flag = 1;
                 ok = false;
             }
-            if (ok && prole == 2 && p.wait_flags && st.valid) {
+            if (kExchange && ok && prole == 2 && p.wait_flags && st.valid) {
                 // the activations come out of an exchange between the GPUs: bounded wait for every rank's rows
                 bool here = lane >= p.wait_n;
                 // the count of consumed exchanges and the first look at the flags travel together (the plain
@@ -786,9 +793,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             uint32_t idx = 0, slot = 0, abuf = 0, ph = 0;
             bool ok = true;
             Walk wk;
-            wk.init(p);
+            wk.template init<kBalanced>(p);
             Item w;
-            while (ok && wk.next(p, w)) {
+            while (ok && wk.template next<kBalanced>(p, w)) {
                 if (w.nk == 0) continue;
                 const uint32_t accbuf = idx % kAccBufs;
                 if (idx >= (uint32_t)kAccBufs)
@@ -832,24 +839,25 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         uint32_t idx = 0;
         bool ok = true;
         Walk wk;
-        wk.init(p);
+        wk.template init<kBalanced>(p);
         Item w;
         const bool leader = warp == kEpilogueWarp0 && lane == 0;
         // Fused exchange: this launch's number and the count of consumed exchanges are read now, long before
         // they are needed (launches on one set of buffers are ordered by the stream, so nobody changes them
         // in between), so that the end of the kernel is a chain of stores without loads.
         uint32_t my_seq = 0, consumed = 0;
-        if (leader && p.done) {
+        if (kExchange && leader && p.done) {
             if (p.n_flags > 0) my_seq = *reinterpret_cast<volatile uint32_t*>(p.sequence) + 1u;
             if (p.wait_flags) consumed = *reinterpret_cast<volatile uint32_t*>(p.wait_flags + p.wait_n + 1) + 1u;
         }
-        while (ok && wk.next(p, w)) {
+        while (ok && wk.template next<kBalanced>(p, w)) {
             const int grow = w.y * 128 + row_in_block;
             // element (col, grow) of this launch's result, in every output buffer
             const size_t out0 = (p.split_k > 1 ? (size_t)w.batch * p.M * p.N : (size_t)0) + (size_t)p.row0 + (size_t)grow;
+            const int n_out = kExchange ? p.n_out : 1;
             auto store = [&](int col, uint16_t v) {
                 const size_t at = out0 + (size_t)col * p.ld_out;
-                for (int q = 0; q < p.n_out; ++q) p.outs[q][at] = v;
+                for (int q = 0; q < n_out; ++q) p.outs[q][at] = v;
             };
             if (w.nk == 0) {
                 for (int n = 0; n < NPAD; ++n) {
@@ -863,7 +871,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             // counter; whoever completes the count adds the sums up in k order, so the result does not
             // depend on who that is, and writes the fp16 result.  Nobody waits for anybody.
             int c_first = 0, c_last = 0, u0 = 0, arrived = 0;
-            if (w.partial) {
+            if ((kBalanced && w.partial)) {
                 const int row = w.nt * p.row_blocks + w.y;
                 u0 = row * p.kt_total + w.batch * p.avg_kt;
                 int u1 = u0 + p.avg_kt;
@@ -879,7 +887,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             ok = mbar_wait_relaxed(bar_accfull + 8 * accbuf, (idx / kAccBufs) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             bool direct = false;
-            if (w.partial) {
+            if ((kBalanced && w.partial)) {
                 if (leader) {
                     // the run may have been long: look again before taking the slower way
                     if (arrived != c_last - c_first) arrived = ld_acquire_gpu(p.counters + w.id);
@@ -893,7 +901,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             tc_fence_after();
             const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + accbuf * (kNAcc * NPAD);
             // the first contributor used its second slot unless its share starts with this range
-            const int slot_first = w.partial && share_begin(p, c_first) != u0 ? 1 : 0;
+            const int slot_first = (kBalanced && w.partial) && share_begin(p, c_first) != u0 ? 1 : 0;
             auto slot_of = [&](int cc) -> float* {
                 return p.partials + (size_t)(2 * cc + (cc == c_first ? slot_first : 0)) * (128 * NPAD) + row_in_block;
             };
@@ -943,7 +951,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 const int col0 = w.nt * NPAD + c * 16;
                 if (grow < p.M) {
 #pragma unroll 1
-                    for (int q = 0; q < p.n_out; ++q) {
+                    for (int q = 0; q < n_out; ++q) {
                         uint16_t* o = p.outs[q] + out0 + (size_t)col0 * p.ld_out;
 #pragma unroll
                         for (int n = 0; n < 16; ++n)
@@ -969,7 +977,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_accempty + 8 * accbuf);
                 }
-                if (!w.partial) {
+                if (!(kBalanced && w.partial)) {
                     float acc[16];
 #pragma unroll
                     for (int n = 0; n < 16; ++n) acc[n] = __uint_as_float(r[n]);
@@ -985,9 +993,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     for (int n = 0; n < 16; ++n) __stcg(mine + (c * 16 + n) * 128, __uint_as_float(r[n]));
                 }
             }
-            if (w.partial && direct) {
+            if ((kBalanced && w.partial) && direct) {
                 if (leader) p.counters[w.id] = 0;  // ready for the next launch
-            } else if (w.partial) {
+            } else if ((kBalanced && w.partial)) {
                 // One thread publishes the CTA's partial sums (its fence covers the stores the barrier
                 // ordered before it) and counts the arrival; its second fence makes the other CTAs' sums
                 // visible to the threads that pass the second barrier.
@@ -1013,7 +1021,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             }
             ++idx;
         }
-        if (p.done) {
+        if (kExchange && p.done) {
             // Fused all-gather: every thread's stores to the peers are made visible system-wide before the CTA
             // counts itself as finished; the CTA that completes the count numbers the launch and tells the peers.
             // (the barrier orders the other threads' stores before the leader's system-scope fence, which is
@@ -1076,9 +1084,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         // others' arithmetic on every scheduler; starting them apart on purpose measured the same.
         bool ok = true;
         Walk wk;
-        wk.init(p);
+        wk.template init<kBalanced>(p);
         Item w;
-        while (ok && wk.next(p, w)) {
+        while (ok && wk.template next<kBalanced>(p, w)) {
             const bool valid = chunk == 0 || (2 * w.y + 1) < p.gm_total;
             for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT) {
                 const int nv = min(kKT, w.nk - kk0);
@@ -1301,7 +1309,8 @@ double balanced_cost(int row_blocks, int n_tiles, int kt, int sk, int sms, int n
         others = others <= 1.0 ? 1.0 : (double)(long)(others + 0.999);
         exchange = 6.0 + 2.2 * (npad / 16) * others;
     }
-    return share + exchange + (sk > 1 ? 3.0 + 0.15 * sk : 0.0);
+    // the balanced variant of the kernel needs about 4 % longer per k-tile than the static one
+    return 1.04 * share + exchange + (sk > 1 ? 3.0 + 0.15 * sk : 0.0);
 }
 bool prefer_balanced(int row_blocks, int n_tiles, int kt, int sk, int sms, int npad)
 {
@@ -1395,12 +1404,17 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
         p.done = sc->counters + kCounterCap;
     }
 
-    static bool attr_set[64] = {false};
-    if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(spmm_bitmap_tcgen05_kernel<NPAD>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
+    const bool exchange = fused || p.wait_flags != nullptr;
+    const int variant = (exchange ? 2 : 0) + (p.balanced ? 1 : 0);
+    auto kernel = variant == 3   ? spmm_bitmap_tcgen05_kernel<NPAD, true, true>
+                  : variant == 2 ? spmm_bitmap_tcgen05_kernel<NPAD, true, false>
+                  : variant == 1 ? spmm_bitmap_tcgen05_kernel<NPAD, false, true>
+                                 : spmm_bitmap_tcgen05_kernel<NPAD, false, false>;
+    static bool attr_set[64][4] = {};
+    if (!attr_set[dev][variant]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
         if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
+        attr_set[dev][variant] = true;
     }
     const long long work = p.balanced ? units : (long long)p.num_items;
     const int grid = work < di.sms ? (int)work : di.sms;
@@ -1416,7 +1430,7 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, spmm_bitmap_tcgen05_kernel<NPAD>, p, tmap);
+    return cudaLaunchKernelEx(&cfg, kernel, p, tmap);
 }
 
 }  // namespace
