@@ -161,7 +161,7 @@ def main():
     ap.add_argument("--case", default=None,
                     help="M,K,N[,sparsity[,split_k]]: time one SpMM shape instead of the OPT-13B set "
                          "(used for per-shape tables and for small profiler captures)")
-    ap.add_argument("--exchange", default="nccl", choices=["peer", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="several GPUs: how the output rows are gathered. peer = the SpMM kernel stores its rows into "
                          "every GPU's buffer over NVLink and the next SpMM waits for the flags itself "
                          "(spb_spmm_bitmap_v3_allgather); nccl = local SpMM, then an NCCL all-gather")
