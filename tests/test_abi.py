@@ -65,3 +65,25 @@ int main(int argc, char**) {
                         "-l:libSpMM_API.so", "-Xlinker", f"-rpath={libdir}"], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     assert subprocess.run([str(exe)]).returncode == 0
+
+
+def test_split_k_suggestion_and_schedule_switch_without_gpu(lib_built):
+    """The suggestion is pure host arithmetic (148 SMs assumed when no device answers): it never leaves an empty
+    last range, and it follows the schedule switch."""
+    from spmspm_b200 import _lib
+    lib = _lib.load()
+    assert lib.spb_set_schedule(0) in (0, 1, 2)
+    for M, N, K in [(28672, 16, 7168), (4096, 16, 4096), (5120, 16, 5120), (5120, 32, 20480), (64, 16, 64), (128, 8, 192),
+                    (15360, 8, 5120), (1152, 16, 36864)]:
+        for mode in (0, 1):
+            lib.spb_set_schedule(mode)
+            sk = lib.spb_suggest_split_k(M, N, K)
+            kt = K // 64
+            assert 1 <= sk <= min(32, kt)
+            avg = (kt - 1) // sk + 1
+            assert (sk - 1) * avg < kt                      # no empty last range
+    lib.spb_set_schedule(1)
+    assert lib.spb_suggest_split_k(28672, 16, 7168) > 1     # static: 224 items on 148 SMs want a split
+    lib.spb_set_schedule(0)
+    assert lib.spb_suggest_split_k(28672, 16, 7168) == 1    # balanced shares fill the SMs without one
+    assert lib.spb_set_schedule(7) == -1 and lib.spb_set_schedule(0) == 0
