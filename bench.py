@@ -161,10 +161,12 @@ def main():
     ap.add_argument("--case", default=None,
                     help="M,K,N[,sparsity[,split_k]]: time one SpMM shape instead of the OPT-13B set "
                          "(used for per-shape tables and for small profiler captures)")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="several GPUs: how the output rows are gathered. peer = the SpMM kernel stores its rows into "
                          "every GPU's buffer over NVLink and the next SpMM waits for the flags itself "
-                         "(spb_spmm_bitmap_v3_allgather); nccl = local SpMM, then an NCCL all-gather")
+                         "(spb_spmm_bitmap_v3_allgather); nccl = local SpMM, then an NCCL all-gather; auto = peer on "
+                         "2 GPUs, where it was measured faster, nccl on more (the fused exchange of this build "
+                         "has not been measured there)")
     ap.add_argument("--schedule", default="auto", choices=["auto", "static", "balanced"],
                     help="work schedule of the SpMM kernel (spb_set_schedule); auto lets the library choose per call")
     args = ap.parse_args()
@@ -228,6 +230,8 @@ def main():
     exchange = "none"
     if world > 1:
         exchange = args.exchange
+        if exchange == "auto":
+            exchange = "peer" if world == 2 else "nccl"
         if exchange == "peer":
             try:
                 # one buffer each: in this chain a buffer is rewritten a whole step after every rank consumed it,
