@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libSpMM_API.so")
+# SPMSPM_B200_LIB names another build of the same library (e.g. one compiled with other tuning constants).
+LIB_PATH = os.environ.get("SPMSPM_B200_LIB") or os.path.join(_HERE, "libSpMM_API.so")
 
 _u16p = ctypes.POINTER(ctypes.c_uint16)
 _i32p = ctypes.POINTER(ctypes.c_int)

@@ -37,7 +37,31 @@
 #include <atomic>
 #include <mutex>
 
+#ifndef SPB_PROBE
+#define SPB_PROBE 0
+#endif
+#ifndef SPB_PROBE_MMAS
+#define SPB_PROBE_MMAS 4  // timing probes only: fewer MMAs per k-tile (wrong results)
+#endif
+#ifndef SPB_PROBE_SKIP
+#define SPB_PROBE_SKIP 0  // timing probes only: copies left out (1 activations, 2 bitmaps and median offsets, 4 values)
+#endif
+#ifndef SPB_PROBE_WAIT
+#define SPB_PROBE_WAIT 0
+#endif
+#ifndef SPB_PROF
+#define SPB_PROF 0  // development only: per-phase clock sums of one decode warp, the MMA warp and a producer warp
+#endif
+#ifndef SPB_PROBE_SEGS
+#define SPB_PROBE_SEGS 8  // timing probes only: fewer row segments per k-tile (wrong results)
+#endif
 namespace spb {
+#if SPB_PROF
+__device__ unsigned long long g_prof[32];
+#define PROF_T(i) do { const uint32_t t_ = clock(); pacc[i] += t_ - plast; plast = t_; } while (0)
+#else
+#define PROF_T(i) do {} while (0)
+#endif
 namespace {
 
 // Warp roles, by warpgroup (4 warps) so that each role can resize its register file share:
@@ -48,8 +72,15 @@ namespace {
 // groups.  (Stages of one or two k-tiles mean more stages in the shared-memory ring and more copies per
 // byte; they measured 1.7x and 1.15x slower.)
 constexpr int kKT = 4;
-constexpr int kDecodeGroups = 4;
-static_assert(kKT == kDecodeGroups, "the decode loop deals the k-tiles of a stage to all groups");
+#ifndef SPB_GROUPS
+#define SPB_GROUPS 6
+#endif
+// Decode groups.  The k-tiles of the CTA's whole sequence are dealt to the groups in turn (k-tile t goes to
+// group t % kDecodeGroups), so a stage gives a group at most one k-tile as long as there are at least kKT groups.
+constexpr int kDecodeGroups = SPB_GROUPS;
+static_assert(kDecodeGroups >= kKT && kDecodeGroups <= 6, "a stage must not give a group two k-tiles; 32 warps at most");
+// A operand blocks in tensor memory (32 columns = one k-tile each), used in turn: k-tile t uses block t % kABlocks.
+constexpr int kABlocks = 8;
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
@@ -59,15 +90,18 @@ constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kDecodeGroups);
 // kernel), and a warp that grows can only take what other warps of the CTA have given back: if the sizes
 // below added up to more than the launch allocation, the last warps to grow would block for ever.
 constexpr int kRegsLaunch = 65536 / kThreads / 8 * 8;
-constexpr int kRegsControl = 40, kRegsEpilogue = 56, kRegsDecode = 96;
+constexpr int kRegsControl = 40, kRegsEpilogue = 56;
+constexpr int kRegsDecode = kDecodeGroups == 4 ? 96 : kDecodeGroups == 5 ? 80 : 64;
 static_assert(kRegsControl % 8 == 0 && kRegsEpilogue % 8 == 0 && kRegsDecode % 8 == 0, "register counts come in eights");
 static_assert(128 * kRegsControl + 128 * kRegsEpilogue + 128 * kDecodeGroups * kRegsDecode <= kRegsLaunch * kThreads,
               "register budget: the resized roles must fit into the CTA's launch allocation");
 static_assert(kRegsControl <= kRegsLaunch && kRegsEpilogue <= kRegsLaunch && kRegsDecode >= kRegsLaunch,
               "roles that shrink must not exceed, roles that grow must not undercut the launch allocation");
+// With six groups the launch allocation (64 registers) is what the decode loop needs: nobody resizes.
+constexpr bool kResize = kRegsDecode > kRegsLaunch;
 constexpr int kMaxPeers = 8;
 constexpr int kMaxStages = 24;
-constexpr int kHeaderBytes = 3072;  // barriers and flags (1 KB), then 128 bytes of tile starts per decode warp
+constexpr int kHeaderBytes = 1024 + 128 * 4 * kDecodeGroups;  // barriers and flags (1 KB), then 128 bytes of tile starts per decode warp
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 
@@ -150,6 +184,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // integer-pipe cycles from the decode warps of the same scheduler.
 __device__ __forceinline__ bool mbar_wait_patient(uint32_t bar, uint32_t parity, volatile int* abort_flag)
 {
+#if SPB_PROBE_WAIT
+    return mbar_wait(bar, parity, abort_flag);
+#endif
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (i >= 4) {
@@ -270,6 +307,12 @@ __device__ __forceinline__ bool bar_and_epilogue(bool pred)
         : "r"((uint32_t)pred)
         : "memory");
     return r != 0;
+}
+// Bits of the nv A operand blocks that follow block tb in the ring of kABlocks.
+__device__ __forceinline__ uint32_t block_mask(uint32_t tb, int nv)
+{
+    const uint32_t m = ((1u << nv) - 1u) << tb;
+    return (m | (m >> kABlocks)) & ((1u << kABlocks) - 1u);
 }
 // A work item is a run of k-tiles of one 128-row block (and one activation tile column): a whole split-K
 // range, or, with the balanced schedule, a piece of one.
@@ -499,6 +542,15 @@ __device__ __forceinline__ void unit_load(uint32_t lo, uint32_t hi, uint32_t til
     u.c67 = __popc(g & 0xc0u);                             // values at positions 6,7
     u.sb = w0 << 3;
     u.st = wt << 3;
+#if SPB_PROBE == 1   // two more population counts (and the integer ops that keep them alive)
+    u.sb += (__popc(lo ^ 0x1234567u) << 5) + (__popc(hi | 0x10204080u) << 6);
+#elif SPB_PROBE == 2  // the same integer ops without the population counts
+    u.sb += ((lo ^ 0x1234567u) << 5) + ((hi | 0x10204080u) << 6);
+#elif SPB_PROBE == 3  // one more conflict-free shared-memory load
+    u.sb += lds32(lut + ((lo ^ 0x1234567u) & 0x3cu)) << 5;
+#elif SPB_PROBE == 4  // eight more integer ops
+    { uint32_t z = lo ^ 0x1234567u; z = (z << 3) ^ hi; z = (z >> 5) + lo; z = (z << 7) ^ hi; z = (z >> 9) + lo; u.sb += z << 5; }
+#endif
 }
 __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
 {
@@ -532,11 +584,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t bar_full = smem_u32(bars);                         // [kMaxStages]
     const uint32_t bar_empty = bar_full + 8 * kMaxStages;             // [kMaxStages]
-    const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [2 * kKT]: A operand (buffer, k-tile) written
-    const uint32_t bar_afree = bar_aready + 8 * 2 * kKT;              // [2 * kKT]: ... read by its MMAs
-    const uint32_t bar_accfull = bar_afree + 8 * 2 * kKT;             // [2]
+    const uint32_t bar_aready = bar_empty + 8 * kMaxStages;           // [kABlocks]: A operand block written
+    const uint32_t bar_afree = bar_aready + 8 * kABlocks;             // [kABlocks]: ... read by its MMAs
+    const uint32_t bar_accfull = bar_afree + 8 * kABlocks;            // [2]
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 4 * kKT + 4));
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kABlocks + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     volatile int* finisher = reinterpret_cast<volatile int*>(tmem_holder + 2);
     const uint32_t stage0 = smem_u32(smem + kHeaderBytes);
@@ -547,16 +599,16 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     constexpr int kNAcc = 4;
     constexpr int kAccBufs = NPAD <= 32 ? 2 : 1;
     constexpr uint32_t kAccCols = kAccBufs * kNAcc * NPAD;
-    constexpr uint32_t kACols = 2 * kKT * 32;  // A operands of two stages
+    constexpr uint32_t kACols = kABlocks * 32;
     static_assert(kAccCols + kACols <= 512, "TMEM budget");
     constexpr uint32_t kTmemCols = 512;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kMaxStages; ++i) {
             mbar_init(bar_full + 8 * i, 1);
-            mbar_init(bar_empty + 8 * i, 4 * kKT + 1);  // every decode warp + the MMA commit
+            mbar_init(bar_empty + 8 * i, 4 * kDecodeGroups + 1);  // every decode warp + the MMA commit
         }
-        for (int i = 0; i < 2 * kKT; ++i) {
+        for (int i = 0; i < kABlocks; ++i) {
             mbar_init(bar_aready + 8 * i, 4);  // the four warps of the group that expanded the k-tile
             mbar_init(bar_afree + 8 * i, 1);   // the commit after the k-tile's MMAs
         }
@@ -617,7 +669,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     // (Nothing above this line needs the stage size, which depends on max_nnz_intile, a load from global
     // memory: the producers below start fetching the tile offsets before they look at it.)
     if (warp < kEpilogueWarp0) {
-        reg_dealloc<kRegsControl>();
+        if constexpr (kResize) reg_dealloc<kRegsControl>();
         if (warp != kMmaWarp) {
             // ================================================================= producers
             // Issuing a bulk copy costs the issuing thread on the order of a hundred cycles, so the
@@ -680,6 +732,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             load_batch(cur);
             Batch nxt = batch_after(cur);
             load_batch(nxt);
+#if SPB_PROF
+            uint32_t pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, plast = clock();
+#endif
             if (S < 1) {
                 // A single stage does not fit (cannot happen with the launch configuration used by the host
                 // code): nothing is copied, the other warps give up on their bounded waits.
@@ -733,9 +788,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 const int a1 = __shfl_sync(0xffffffffu, cur.v1, bidx), e1 = __shfl_sync(0xffffffffu, cur.v1, bidx + nv);
                 const int r0 = __shfl_sync(0xffffffffu, cur.v0, bidx + (lane & 7));
                 const int r1 = __shfl_sync(0xffffffffu, cur.v1, bidx + (lane & 7));
+                PROF_T(0);
                 if (round > 0) ok = mbar_wait_patient(bar_empty + 8 * slot, (round - 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                PROF_T(1);
                 uint32_t n0 = (uint32_t)(e0 - a0) * 2, n1 = chunk1 ? (uint32_t)(e1 - a1) * 2 : 0u;
                 if (e0 < a0 || n0 > (uint32_t)nv * vmax || (chunk1 && (e1 < a1 || n1 > (uint32_t)nv * vmax))) {
                     if (lane == 0 && prole == 0) atomicOr(p.status, (int)kStatusBadOffsets);
@@ -757,11 +814,19 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 // one elected lane issues this warp's copies with warp-uniform operands
                 if (elect_one()) {
                     if (prole == 0) {
+#if SPB_PROBE_SKIP
+                        if (SPB_PROBE_SKIP & 4) { n0 = 0; n1 = 0; }
+                        const uint32_t tx = ((SPB_PROBE_SKIP & 1) ? 0u : (uint32_t)nv * kBTile) + n0 + n1 +
+                                            ((SPB_PROBE_SKIP & 2) ? 0u : (chunk1 ? 2u : 1u) * (uint32_t)nv * (512u + 16u));
+#else
                         const uint32_t tx =
                             (uint32_t)nv * kBTile + n0 + n1 + (chunk1 ? 2u : 1u) * (uint32_t)nv * (512u + 16u);
+#endif
                         mbar_expect_tx(full, tx);
                         if (n0) bulk_g2s(sbase + off_v0, p.vals + a0, n0, full);
                         if (n1) bulk_g2s(sbase + off_v1, p.vals + a1, n1, full);
+                    } else if ((SPB_PROBE_SKIP & 2) && prole == 1) {
+                    } else if ((SPB_PROBE_SKIP & 1) && prole == 2) {
                     } else if (prole == 1) {
                         bulk_g2s(sbase + off_bm0, p.bitmap + g0 * 64, (uint32_t)nv * 512u, full);
                         bulk_g2s(sbase + off_mt0, p.mtile + g0 * 4, (uint32_t)nv * 16u, full);
@@ -780,7 +845,17 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     slot = 0;
                     ++round;
                 }
+                PROF_T(2);
+#if SPB_PROF
+                ++pacc[7];
+#endif
             }
+#if SPB_PROF
+            if (lane == 0) {
+                for (int i = 0; i < 3; ++i) atomicAdd(&g_prof[12 + 4 * prole + i], (unsigned long long)pacc[i]);
+                atomicAdd(&g_prof[12 + 4 * prole + 3], (unsigned long long)pacc[7]);
+            }
+#endif
         } else if (warp == kMmaWarp) {
             // ================================================================= MMA issuer
             // The whole warp runs the loop with warp-uniform state (so addresses and descriptors stay
@@ -790,11 +865,14 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             // the decode groups that the block may be rewritten; the last one of a stage also arrives on
             // the stage's empty barrier, for the producers.
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            uint32_t idx = 0, slot = 0, abuf = 0, ph = 0;
+            uint32_t idx = 0, slot = 0, tb = 0, ph = 0;  // tb: block of the stage's first k-tile
             bool ok = true;
             Walk wk;
             wk.template init<kBalanced>(p);
             Item w;
+#if SPB_PROF
+            uint32_t pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, plast = clock();
+#endif
             while (ok && wk.template next<kBalanced>(p, w)) {
                 if (w.nk == 0) continue;
                 const uint32_t accbuf = idx % kAccBufs;
@@ -806,33 +884,40 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     const int nv = min(kKT, w.nk - kk0);
                     const uint32_t sbase = stage0 + slot * stage_bytes;
                     for (int sub = 0; sub < nv && ok; ++sub) {
-                        const uint32_t blk = abuf * kKT + (uint32_t)sub;
+                        const uint32_t blk = (tb + (uint32_t)sub) % kABlocks;
+                        PROF_T(0);
                         ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_aready + 8 * blk, (ph >> blk) & 1u, abort_flag));
                         if (!ok) break;
+                        PROF_T(1);
                         tc_fence_after();
                         if (elect_one()) {
                             const uint64_t bdesc = make_b_desc(sbase + (uint32_t)sub * kBTile);
                             const uint32_t a_tmem = tmem_a0 + blk * 32;
 #pragma unroll
-                            for (int s = 0; s < 4; ++s)
+                            for (int s = 0; s < SPB_PROBE_MMAS; ++s)
                                 tc_mma_ts(d_tmem + (s % kNAcc) * NPAD, a_tmem + 8 * s, bdesc + 2 * s, idesc,
                                           (kk0 > 0 || sub > 0 || s >= kNAcc) ? 1u : 0u);
                             tc_commit(bar_afree + 8 * blk);
                             if (sub == nv - 1) tc_commit(bar_empty + 8 * slot);
                         }
                         __syncwarp();
+                        PROF_T(2);
                     }
-                    ph ^= ((1u << nv) - 1u) << (abuf * kKT);
+                    ph ^= block_mask(tb, nv);
+                    tb = (tb + (uint32_t)nv) % kABlocks;
                     if (++slot == (uint32_t)S) slot = 0;
-                    abuf ^= 1u;
                 }
                 if (ok && elect_one()) tc_commit(bar_accfull + 8 * accbuf);
                 __syncwarp();
                 ++idx;
             }
+#if SPB_PROF
+            if (lane == 0)
+                for (int i = 0; i < 3; ++i) atomicAdd(&g_prof[8 + i], (unsigned long long)pacc[i]);
+#endif
         }
     } else if (warp < kDecodeWarp0) {
-        reg_dealloc<kRegsEpilogue>();
+        if constexpr (kResize) reg_dealloc<kRegsEpilogue>();
         // ================================================================= epilogue
         const int quad = warp & 3;
         const int row_in_block = quad * 32 + lane;
@@ -1047,10 +1132,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         // crosses 8 bitmap tiles per k-tile; the thread reads their bitmaps, keeps a running sum of the
         // tile sizes inside its 16-row median tile (the other tile of each pair is counted by the lane
         // 8 away), finds its row's values with popcounts and expands them.
-        reg_alloc<kRegsDecode>();
+        if constexpr (kResize) reg_alloc<kRegsDecode>();
         const int dw = warp - kDecodeWarp0;
         const int group = dw >> 2;
-        const int gsub = group % kKT;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;      // weight row inside the 128-row block
         const uint32_t lut = smem_u32(lut_tab);
@@ -1076,7 +1160,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         // The k-tiles of the stages are dealt to the groups in turn, across stages and work items: k-tile j of
         // a stage goes to group (j + rot) % kKT, rot = k-tiles dealt so far.  A stage with fewer than kKT
         // k-tiles (the end of a work item) then costs no more than the k-tiles it has.
-        uint32_t slot = 0, round = 0, rot = 0, abuf = 0, ph = 0, used = 0;
+        uint32_t slot = 0, round = 0, rot = 0, tb = 0, ph = 0, used = 0;
         const uint32_t tsel = tile_tab + tile_sel;
         // The start of a k-tile (barrier checks, tile starts) is a chain of dependent instructions, its body is
         // bound by arithmetic throughput.  Because no group ever waits for another one (see the A block
@@ -1086,18 +1170,23 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         Walk wk;
         wk.template init<kBalanced>(p);
         Item w;
+#if SPB_PROF
+        uint32_t pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, plast = clock();
+#endif
         while (ok && wk.template next<kBalanced>(p, w)) {
             const bool valid = chunk == 0 || (2 * w.y + 1) < p.gm_total;
             for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT) {
                 const int nv = min(kKT, w.nk - kk0);
-                const int sub = (int)(((uint32_t)gsub + (uint32_t)kKT - rot) % (uint32_t)kKT);  // this group's k-tile
-                rot = (rot + (uint32_t)nv) % (uint32_t)kKT;
-                const uint32_t blk = abuf * kKT + (uint32_t)sub;
+                const int sub = (int)(((uint32_t)group + (uint32_t)kDecodeGroups - rot) % (uint32_t)kDecodeGroups);  // this group's k-tile
+                rot = (rot + (uint32_t)nv) % (uint32_t)kDecodeGroups;
+                const uint32_t blk = (tb + (uint32_t)sub) % kABlocks;
                 // Every group, with or without a k-tile, waits for the stage: it arrives on the stage's empty
                 // barrier below and must not get a ring round ahead of it.
+                PROF_T(0);
                 ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                PROF_T(1);
                 if (sub < nv) {
                     const uint32_t st = stage0 + slot * stage_bytes;
                     {   // starts of the warp's 32 tiles: running sum of the tile sizes inside each median tile
@@ -1121,16 +1210,18 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                                      : "memory");
                         __syncwarp();
                     }
+                    PROF_T(2);
                     // the MMAs of the block's previous k-tile (they ran while the tile starts were worked out)
                     if ((used >> blk) & 1u) ok = mbar_wait(bar_afree + 8 * blk, ((ph >> blk) & 1u) ^ 1u, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
+                    PROF_T(3);
                     const uint32_t ta = tmem_a0 + blk * 32 + ((uint32_t)(quad * 32) << 16);
                     const uint32_t sp_bm = st + bm0 + (uint32_t)sub * 512;
                     uint32_t a[32];
 #pragma unroll
-                    for (int q0 = 0; q0 < 8; q0 += 2) {
+                    for (int q0 = 0; q0 < SPB_PROBE_SEGS; q0 += 2) {
                         uint32_t blo[2], bhi[2];
                         UnitLoads u[2];
 #pragma unroll
@@ -1145,24 +1236,34 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         for (int q = 0; q < 2; ++q) unit_expand(u[q], a + 4 * (q0 + q));
                         tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
                     }
+                    PROF_T(4);
                     tc_wait_st();
                     tc_fence_before();
+                    PROF_T(5);
+#if SPB_PROF
+                    ++pacc[7];
+#endif
                 }
                 __syncwarp();
                 if (lane == 0) {
                     if (sub < nv) mbar_arrive(bar_aready + 8 * blk);
                     mbar_arrive(bar_empty + 8 * slot);
                 }
-                const uint32_t mask = ((1u << nv) - 1u) << (abuf * kKT);
+                const uint32_t mask = block_mask(tb, nv);
                 used |= mask;
                 ph ^= mask;
-                abuf ^= 1u;
+                tb = (tb + (uint32_t)nv) % kABlocks;
                 if (++slot == (uint32_t)S) {
                     slot = 0;
                     ++round;
                 }
+                PROF_T(6);
             }
         }
+#if SPB_PROF
+        if (dw == 0 && lane == 0)
+            for (int i = 0; i < 8; ++i) atomicAdd(&g_prof[i], (unsigned long long)pacc[i]);
+#endif
     }
 
     // ---- teardown ----------------------------------------------------------------------------
@@ -1450,6 +1551,19 @@ cudaError_t exchange_counter(cudaStream_t s, int** out)
     return cudaSuccess;
 }
 
+#if SPB_PROF
+}  // namespace spb
+extern "C" int spb_debug_prof(unsigned long long* out, int clear)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, spb::g_prof, sizeof(unsigned long long) * 32);
+    if (e == cudaSuccess && clear) {
+        unsigned long long z[32] = {};
+        e = cudaMemcpyToSymbol(spb::g_prof, z, sizeof(z));
+    }
+    return (int)e;
+}
+namespace spb {
+#endif
 int set_schedule(int mode)
 {
     if (mode < 0 || mode > 2) return -1;
