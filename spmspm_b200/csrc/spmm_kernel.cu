@@ -52,6 +52,9 @@
 #ifndef SPB_PROF
 #define SPB_PROF 0  // development only: per-phase clock sums of one decode warp, the MMA warp and a producer warp
 #endif
+#ifndef SPB_SEG3
+#define SPB_SEG3 1  // row segments driven by a per-tile table entry (bitmap half + start of the half's values) and a byte-indexed selector table
+#endif
 #ifndef SPB_PROBE_SEGS
 #define SPB_PROBE_SEGS 8  // timing probes only: fewer row segments per k-tile (wrong results)
 #endif
@@ -73,7 +76,7 @@ namespace {
 // byte; they measured 1.7x and 1.15x slower.)
 constexpr int kKT = 4;
 #ifndef SPB_GROUPS
-#define SPB_GROUPS 6
+#define SPB_GROUPS 4
 #endif
 // Decode groups.  The k-tiles of the CTA's whole sequence are dealt to the groups in turn (k-tile t goes to
 // group t % kDecodeGroups), so a stage gives a group at most one k-tile as long as there are at least kKT groups.
@@ -101,7 +104,20 @@ static_assert(kRegsControl <= kRegsLaunch && kRegsEpilogue <= kRegsLaunch && kRe
 constexpr bool kResize = kRegsDecode > kRegsLaunch;
 constexpr int kMaxPeers = 8;
 constexpr int kMaxStages = 24;
-constexpr int kHeaderBytes = 1024 + 128 * 4 * kDecodeGroups;  // barriers and flags (1 KB), then 128 bytes of tile starts per decode warp
+// Shared-memory header: barriers and flags (1 KB), one tile table per decode warp, then the selector table.
+//   tile table   32 entries (the warp's tiles of the k-tile it is expanding) of 16 bytes:
+//                {bitmap rows 0-3, address of the first value of rows 0-3, bitmap rows 4-7, address of the first value of rows 4-7}
+//   selector table  indexed by a row's 8-bit mask: {low-nibble entry, high-nibble entry} (see lut_low_entry), 16 copies
+//                interleaved so that the 16 lanes of a half warp always read 16 different 8-byte slots
+#if SPB_SEG3
+constexpr int kTileTabBytes = 512;
+constexpr int kLutBytes = 256 * 16 * 8;
+#else
+constexpr int kTileTabBytes = 128;
+constexpr int kLutBytes = 0;
+#endif
+constexpr int kHeaderBytes = 1024 + kTileTabBytes * 4 * kDecodeGroups + kLutBytes;
+static_assert(kHeaderBytes % 1024 == 0, "the stages behind the header must stay 1024-byte aligned");
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 
@@ -552,6 +568,25 @@ __device__ __forceinline__ void unit_load(uint32_t lo, uint32_t hi, uint32_t til
     { uint32_t z = lo ^ 0x1234567u; z = (z << 3) ^ hi; z = (z >> 5) + lo; z = (z << 7) ^ hi; z = (z >> 9) + lo; u.sb += z << 5; }
 #endif
 }
+// The same from a tile table entry: w = bitmap of the tile's rows 0-3 or 4-7 (the half this thread's row is in),
+// half = shared address of the first value of that half.
+//   below   thread constant: bitmap bits of the rows of the half above this thread's row
+//   rsel    permute selector moving this row's mask byte to byte 0 of a zero word
+//   lutlane shared address of this lane's copy of the selector table
+__device__ __forceinline__ void unit_load3(uint32_t w, uint32_t half, uint32_t below, uint32_t rsel, uint32_t lutlane,
+                                           UnitLoads& u)
+{
+    const uint32_t w0 = half + 2u * __popc(w & below);
+    const uint32_t g = prmt(w, 0u, rsel);                  // row mask, zero-extended
+    const uint32_t wt = w0 + 2u * __popc(g);               // address just past the row's last value
+    lds32x3(w0 & ~3u, u.x0, u.x1, u.x2);
+    lds32x3_before(wt & ~3u, u.y0, u.y1, u.y2);            // window of the 4 values before wt
+    lds64(lutlane + g * 128u, u.l, u.h);
+    u.c01 = __popc(g & 3u);                                // values at positions 0,1
+    u.c67 = __popc(g & 0xc0u);                             // values at positions 6,7
+    u.sb = w0 << 3;
+    u.st = wt << 3;
+}
 __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
 {
     const uint32_t b0 = __funnelshift_r(u.x0, u.x1, u.sb), b1 = __funnelshift_r(u.x1, u.x2, u.sb);
@@ -619,10 +654,18 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+#if SPB_SEG3
+    for (uint32_t i = threadIdx.x; i < 256u * 16u; i += kThreads) {
+        const uint32_t g = i >> 4;
+        *reinterpret_cast<uint2*>(smem + 1024 + kTileTabBytes * 4 * kDecodeGroups + 8 * i) =
+            make_uint2(lut_low_entry(g & 15u), lut_high_entry(g >> 4));
+    }
+#else
     if (threadIdx.x >= 32 && threadIdx.x < 64) {
         const uint32_t n = threadIdx.x - 32;
         lut_tab[n] = n < 16 ? lut_low_entry(n) : lut_high_entry(n - 16);
     }
+#endif
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
                      "r"(kTmemCols)
@@ -1149,7 +1192,14 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         // Lane l also looks after one of the 32 tiles of the warp's two median tiles per k-tile (tile l & 15 of
         // median tile 2 * (quad & 1) + (l >> 4)): it works out where the tile's values start and leaves that in
         // the warp's table, from which the row threads read the starts of the tiles they cross.
-        const uint32_t tile_tab = smem_u32(smem + 1024) + (uint32_t)dw * 128;
+        const uint32_t tile_tab = smem_u32(smem + 1024) + (uint32_t)dw * kTileTabBytes;
+#if SPB_SEG3
+        // this row's entry of the table for its first tile (the others are 32 bytes apart), the half its row is in
+        const uint32_t ent = tile_tab + 16 * (uint32_t)(16 * (lane >> 4) + ((lane >> 3) & 1)) + 8 * (uint32_t)(r_in_tile >> 2);
+        const uint32_t below = (r_in_tile & 3) ? (1u << (8 * (r_in_tile & 3))) - 1u : 0u;
+        const uint32_t rsel4 = 0x4440u | (uint32_t)(r_in_tile & 3);
+        const uint32_t lutlane = smem_u32(smem + 1024 + kTileTabBytes * 4 * kDecodeGroups) + 8 * (uint32_t)(lane & 15);
+#endif
         const uint32_t tile_bm0 = (chunk ? off_bm1 : off_bm0) + 8 * (uint32_t)(32 * (quad & 1) + lane);
         const uint32_t tile_mt0 = (chunk ? off_mt1 : off_mt0) + 4 * (uint32_t)(2 * (quad & 1) + (lane >> 4));
         const uint32_t tile_sel = 4 * (uint32_t)(16 * (lane >> 4) + ((lane >> 3) & 1));  // offset inside a table
@@ -1206,8 +1256,17 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                             if ((lane & 15) >= d) x += y;
                         }
                         __syncwarp();  // every lane has read the previous k-tile's table
+#if SPB_SEG3
+                        {
+                            const uint32_t ts_lo = base + 2 * (x - cnt), ts_hi = ts_lo + 2 * __popc(lo);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_tab + 16 * (uint32_t)lane), "r"(lo),
+                                         "r"(ts_lo), "r"(hi), "r"(ts_hi)
+                                         : "memory");
+                        }
+#else
                         asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile_tab + 4 * (uint32_t)lane), "r"(base + 2 * (x - cnt))
                                      : "memory");
+#endif
                         __syncwarp();
                     }
                     PROF_T(2);
@@ -1221,6 +1280,19 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     const uint32_t sp_bm = st + bm0 + (uint32_t)sub * 512;
                     uint32_t a[32];
 #pragma unroll
+#if SPB_SEG3
+                    for (int q0 = 0; q0 < SPB_PROBE_SEGS; q0 += 2) {
+                        uint32_t wq[2], hq[2];
+                        UnitLoads u[2];
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) lds64(ent + 32 * (q0 + q), wq[q], hq[q]);
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) unit_load3(wq[q], hq[q], below, rsel4, lutlane, u[q]);
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) unit_expand(u[q], a + 4 * (q0 + q));
+                        tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
+                    }
+#else
                     for (int q0 = 0; q0 < SPB_PROBE_SEGS; q0 += 2) {
                         uint32_t blo[2], bhi[2];
                         UnitLoads u[2];
@@ -1236,6 +1308,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         for (int q = 0; q < 2; ++q) unit_expand(u[q], a + 4 * (q0 + q));
                         tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
                     }
+#endif
                     PROF_T(4);
                     tc_wait_st();
                     tc_fence_before();
