@@ -1,18 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the bitmap-v3 SpMM path.
 
-A step is one pass over the OPT-13B layer-shaped SpMM set (four weight matrices at 60 %
-uniform-random sparsity, each multiplied at N = 8, 16 and 32: twelve SpMMs), the configuration
-the headline metric is quoted on.  Inputs are synthetic and seeded.  With more than one GPU each
-weight matrix is split by rows across the ranks (tensor-parallel M-split) and the output rows
-are all-gathered over NCCL, so the total work is fixed ("strong" scaling).
+A step is one pass over a set of layer-shaped SpMMs.  The default workload is the OPT-13B layer set (four weight
+matrices at 60 % uniform-random sparsity, each multiplied at N = 8, 16 and 32: twelve SpMMs), the configuration
+the headline metric is quoted on; `--workload opt66b_tp` is the OPT-66B set at N = 16 (four SpMMs) whose row shards
+are checked bit for bit against the CPU encoder inside the run.  Inputs are synthetic and seeded.  With more than
+one GPU each weight matrix is split by rows across the ranks (tensor-parallel M-split) and the output rows are
+gathered on every rank, so the total work is fixed ("strong" scaling).
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME | --case M,K,N[,s[,sk]]]
 
 Prints one JSON line (rank 0).
 """
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -26,11 +28,21 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
+WORKLOADS = {
+    # QKV, out-proj, FC1, FC2
+    "opt13b_layer_set_s60": {"shapes": [(15360, 5120), (5120, 5120), (20480, 5120), (5120, 20480)], "ns": [8, 16, 32],
+                             "sparsity": 0.6},
+    "opt66b_tp": {"shapes": [(27648, 9216), (9216, 9216), (36864, 9216), (9216, 36864)], "ns": [16], "sparsity": 0.6},
+}
 WORKLOAD = "opt13b_layer_set_s60"
-SHAPES = [(15360, 5120), (5120, 5120), (20480, 5120), (5120, 20480)]  # QKV, out-proj, FC1, FC2
-NS = [8, 16, 32]
-SPARSITY = 0.6
+SHAPES = WORKLOADS[WORKLOAD]["shapes"]
+NS = WORKLOADS[WORKLOAD]["ns"]
+SPARSITY = WORKLOADS[WORKLOAD]["sparsity"]
 SEED = 0x5EED0001
+REL_TOL = 1e-2   # max |c - ref| / max |ref| against the fp32 host GEMM
+# Split_K the reference's converter assigns by M (end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:23);
+# used for the reference-style comparator kernel
+REF_SPLIT_K = {4096: 6, 12288: 2, 16384: 2, 5120: 6, 15360: 2, 20480: 3, 7680: 4, 10240: 2, 7168: 4, 21504: 3, 28672: 1}
 
 
 def gen_weight(M, K, idx, device):
@@ -110,27 +122,61 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+def traffic_ratio():
+    """dram bytes / algorithmic bytes of the SpMM kernel in the committed profiler capture (profiles/)."""
+    path = os.path.join(ROOT, "profiles", "spmm_dram_traffic.json")
+    try:
+        d = json.load(open(path))
+        return float(d["dram_bytes"]) / float(d["algorithmic_bytes"]), d.get("capture", "profiles/spmm_dram_traffic.json")
+    except Exception:
+        return None, None
+
+
 def flops_per_step():
     return sum(2.0 * M * K * N for (M, K) in SHAPES for N in NS)
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 # ------------------------------------------------------------------------------------- reference arm
 
 def run_reference(args, rank):
-    """The path on the host cores: decode of the bitmap format + fp32 GEMM (OpenMP), the CPU restatement of the
-    reference's algorithm (the reference ships no CPU SpMM; its own CPU code on this path is the encoder)."""
+    """The path on the host cores: decode of the bitmap format + fp32 GEMM (OpenMP, every core of the box), the CPU
+    restatement of the reference's algorithm (the reference ships no CPU SpMM; its own CPU code on this path is the
+    encoder).  A step is the whole set when that fits the time budget, else the same set on a slab of rows of
+    every matrix (the rate does not depend on the number of rows)."""
     if rank != 0:
         return
     import oracle
-    M, K = SHAPES[1]
-    A = gen_weight(M, K, 1, "cpu").numpy()
-    enc = oracle.encode(A)
-    Bs = [gen_act(N, K, 1, "cpu").numpy() for N in NS]
-    flops = sum(2.0 * M * K * N for N in NS)
+    cores = oracle.set_num_threads(host_threads())   # a launcher may have exported OMP_NUM_THREADS=1
+    budget_s = 120.0
+    total_steps = max(args.warmup, 1) + args.steps
+    # calibrate on 512 rows of the first matrix
+    M0, K0 = SHAPES[0]
+    A0 = gen_weight(min(M0, 512), K0, 0, "cpu").numpy()
+    e0 = oracle.encode(A0)
+    B0 = gen_act(NS[0], K0, 0, "cpu").numpy()
+    oracle.spmm_f32(e0, B0)
+    t0 = time.perf_counter()
+    oracle.spmm_f32(e0, B0)
+    rate = 2.0 * A0.shape[0] * K0 * NS[0] / max(time.perf_counter() - t0, 1e-6)
+    frac = min(1.0, budget_s * rate / (flops_per_step() * total_steps))
+    mats, flops = [], 0.0
+    for i, (M, K) in enumerate(SHAPES):
+        rows = M if frac >= 1.0 else max(64, int(M * frac) // 64 * 64)
+        A = gen_weight(rows, K, i, "cpu").numpy()
+        mats.append((oracle.encode(A), [gen_act(N, K, i, "cpu").numpy() for N in NS]))
+        flops += sum(2.0 * rows * K * N for N in NS)
 
     def step():
-        for B in Bs:
-            oracle.spmm_f32(enc, B)
+        for enc, Bs in mats:
+            for B in Bs:
+                oracle.spmm_f32(enc, B)
 
     for _ in range(max(args.warmup, 1)):
         step()
@@ -139,13 +185,14 @@ def run_reference(args, rank):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     val = flops / dt / 1e12
-    sample = f"out-proj matrix {M}x{K} at N={NS} per step (1 of the 4 matrices of the set)"
+    sample = ("the whole set per step" if frac >= 1.0 else
+              f"the first {frac * 100:.1f} % of the rows of every matrix of the set per step "
+              f"({flops / 1e9:.1f} of {flops_per_step() / 1e9:.1f} GFLOP)")
     line = {"impl": "reference", "metric": "spmm_dense_equiv_tflops", "value": val, "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "config": {"workload": WORKLOAD, "sparsity": SPARSITY, "N": NS, "shapes": SHAPES},
-            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
-                             "sample": sample},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -158,19 +205,24 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="opt13b_layer_set_s60", choices=sorted(WORKLOADS),
+                    help="opt13b_layer_set_s60: the headline set; opt66b_tp: the OPT-66B shapes at N = 16 with every "
+                         "row shard's encoding checked against the CPU encoder inside the run")
     ap.add_argument("--case", default=None,
-                    help="M,K,N[,sparsity[,split_k]]: time one SpMM shape instead of the OPT-13B set "
+                    help="M,K,N[,sparsity[,split_k]]: time one SpMM shape instead of a set "
                          "(used for per-shape tables and for small profiler captures)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="several GPUs: how the output rows are gathered. peer = the SpMM kernel stores its rows into "
                          "every GPU's buffer over NVLink and the next SpMM waits for the flags itself "
-                         "(spb_spmm_bitmap_v3_allgather); nccl = local SpMM, then an NCCL all-gather; auto = peer on "
-                         "2 GPUs, where it was measured faster, nccl on more (the fused exchange of this build "
-                         "has not been measured there)")
+                         "(spb_spmm_bitmap_v3_allgather); nccl = local SpMM, then an NCCL all-gather; auto = both are "
+                         "timed for a few steps and the faster one is used")
     ap.add_argument("--schedule", default="auto", choices=["auto", "static", "balanced"],
                     help="work schedule of the SpMM kernel (spb_set_schedule); auto lets the library choose per call")
+    ap.add_argument("--no-extras", action="store_true", help="skip comparators, CPU baseline and encoder timing")
     args = ap.parse_args()
     global SHAPES, NS, SPARSITY, WORKLOAD
+    WORKLOAD = args.workload
+    SHAPES, NS, SPARSITY = (WORKLOADS[WORKLOAD][k] for k in ("shapes", "ns", "sparsity"))
     forced_split = None
     if args.case:
         f = args.case.split(",")
@@ -201,16 +253,45 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    l2_bytes = int(torch.cuda.get_device_properties(dev).L2_cache_size)
 
     # ---- weights: generate, encode on the GPU, keep only this rank's row shard
     mats = []
+    shard_check = None
     for i, (M, K) in enumerate(SHAPES):
         A = gen_weight(M, K, i, dev)
         lo, hi = spd.row_shard_bounds(M, world, rank)
-        W = sp.encode_device(A[lo:hi].contiguous())
+        shard = A[lo:hi].contiguous()
         del A
+        W = sp.encode_device(shard)
+        if args.workload == "opt66b_tp" and not args.case:
+            # the shard's encoding against the CPU restatement of the reference encoder on the same sub-matrix
+            import oracle
+            e = oracle.encode(shard.cpu().numpy())
+            same = (np.array_equal(W.vals.cpu().numpy().view(np.uint16), e.vals)
+                    and np.array_equal(W.gtile.cpu().numpy(), e.gtile) and np.array_equal(W.mtile.cpu().numpy(), e.mtile)
+                    and np.array_equal(W.bitmap.cpu().numpy().view(np.uint64), e.bitmap)
+                    and np.array_equal(W.tile_nnz.cpu().numpy(), e.tile_nnz) and int(W.max_nnz.item()) == e.max_nnz)
+            shard_check = (shard_check if shard_check is not None else True) and bool(same)
+        del shard
         mats.append(W)
     torch.cuda.empty_cache()
+    if shard_check is not None and world > 1:
+        t = torch.tensor([1 if shard_check else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        shard_check = bool(t.item())
+    weight_bytes = sum(2 * W.val_count + 8 * (W.M * W.K // 64) + 20 * W.G for W in mats)
+    # Rotation: enough copies of this rank's weights that the bytes streamed between two uses of the same copy exceed
+    # twice the L2 capacity at every world size (one copy is enough when the set itself is that large).
+    copies = 1 if args.case else max(1, math.ceil(2.0 * l2_bytes / max(weight_bytes, 1)))
+    copies = min(copies, 16)
+
+    def clone(W):
+        return sp.BitmapMatrix(W.M, W.K, W.vals.clone(), W.gtile.clone(), W.mtile.clone(), W.bitmap.clone(),
+                               W.max_nnz.clone(), None, W.val_count)
+
+    mat_sets = [mats] + [[clone(W) for W in mats] for _ in range(copies - 1)]
+    rotating = copies * weight_bytes > 2 * l2_bytes
     acts = {(i, N): gen_act(N, K, i, dev) for i, (M, K) in enumerate(SHAPES) for N in NS}
     splits = {(i, N): forced_split or sp.suggest_split_k(mats[i].M, N, mats[i].K)
               for i in range(len(SHAPES)) for N in NS}
@@ -221,36 +302,31 @@ def main():
     order = [(i, N) for N in NS for i in range(len(SHAPES))]
     launches_per_step = sum(1 + (1 if splits[k] > 1 else 0) for k in order)
     alg_bytes_step = sum(mats[i].algorithmic_bytes(N) for (i, N) in order)
-    weight_bytes = sum(2 * W.val_count + 8 * (W.M * W.K // 64) + 20 * W.G for W in mats)
 
-    # Several GPUs, peer exchange: one pair of symmetric output buffers per SpMM of the step; every SpMM waits
-    # (inside its kernel) for the exchange of the SpMM before it, as a chain of layers would, the first one of a
-    # step for the last one of the step before.
+    # Several GPUs, peer exchange: one symmetric output buffer per SpMM of the step; every SpMM waits (inside its
+    # kernel) for the exchange of the SpMM before it, as a chain of layers would, the first one of a step for the
+    # last one of the step before.
     peer = None
-    exchange = "none"
-    if world > 1:
-        exchange = args.exchange
-        if exchange == "auto":
-            exchange = "peer" if world == 2 else "nccl"
-        if exchange == "peer":
-            try:
-                # one buffer each: in this chain a buffer is rewritten a whole step after every rank consumed it,
-                # and a captured step then names the same buffers on every replay
-                peer = {k: spd.PeerGather(k[1], SHAPES[k[0]][0], dev, slots=1) for k in order}
-            except Exception as exc:
-                print(f"[bench] symmetric memory unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
-                exchange = "nccl"
+    if world > 1 and args.exchange in ("auto", "peer"):
+        try:
+            # one buffer each: in this chain a buffer is rewritten a whole step after every rank consumed it,
+            # and a captured step then names the same buffers on every replay
+            peer = {k: spd.PeerGather(k[1], SHAPES[k[0]][0], dev, slots=1) for k in order}
+        except Exception as exc:
+            print(f"[bench] symmetric memory unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
     row_lo = {i: spd.row_shard_bounds(SHAPES[i][0], world, rank)[0] for i in range(len(SHAPES))}
     chain = {"prev": None}
 
-    def step():
+    def step_peer(c=0):
         for k in order:
             i, N = k
-            if peer is not None:
-                peer[k].spmm(mats[i], acts[k], row_lo[i], after=chain["prev"], split_k=splits[k], workspace=ws)
-                chain["prev"] = peer[k]
-                continue
-            sp.spmm(mats[i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
+            peer[k].spmm(mat_sets[c][i], acts[k], row_lo[i], after=chain["prev"], split_k=splits[k], workspace=ws)
+            chain["prev"] = peer[k]
+
+    def step_local(c=0):
+        for k in order:
+            i, N = k
+            sp.spmm(mat_sets[c][i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
             if world > 1:
                 dist.all_gather_into_tensor(gathered[k], outs[k])
 
@@ -261,11 +337,12 @@ def main():
             torch.cuda.synchronize()
 
     def timed(fn, steps):
+        """Event time of `steps` calls of fn(i), max over the ranks, in ms."""
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            fn()
+        for i in range(steps):
+            fn(i)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
@@ -275,43 +352,97 @@ def main():
             ms = float(t.item())
         return ms
 
-    # The step (its 12 SpMM calls and, on several GPUs, their all-gathers) is captured once into a CUDA graph and
-    # replayed, so that the host's call overhead is not part of the device-resident number; the eager figure
-    # is reported beside it.
     work = torch.cuda.Stream()
+    exchange = "none"
+    step = step_local
+    exchange_probe = None
+    if world > 1:
+        exchange = "nccl"
+        if peer is not None:
+            exchange = "peer"
+            if args.exchange == "auto":
+                # both ways of gathering are timed for a few steps; the faster one (max over ranks) is used
+                probe = {}
+                for name, fn in (("nccl", step_local), ("peer", step_peer)):
+                    with torch.cuda.stream(work):
+                        for _ in range(3):
+                            fn(0)
+                        probe[name] = timed(lambda i, fn=fn: fn(i % copies), 6) / 6
+                    work.synchronize()
+                exchange = min(probe, key=probe.get)
+                exchange_probe = probe
+        step = step_peer if exchange == "peer" else step_local
+
+    # The step (its SpMM calls and, on several GPUs, their exchanges) is captured once per weight copy into a CUDA
+    # graph and replayed in rotation, so that the host's call overhead is not part of the device-resident number; the
+    # eager figure is reported beside it.
     with torch.cuda.stream(work):
-        for _ in range(args.warmup):
-            step()
+        for w_ in range(args.warmup):
+            step(w_ % copies)
     work.synchronize()
     with torch.cuda.stream(work):
-        eager_ms = timed(step, args.steps) / args.steps
+        eager_ms = timed(lambda i: step(i % copies), args.steps) / args.steps
     timed_as = "cuda_graph_replay"
     try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=work):
-            step()
-        for _ in range(args.warmup):
-            graph.replay()
-        run = graph.replay
+        graphs = []
+        for c in range(copies):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=work):
+                step(c)
+            graphs.append(g)
+        for w_ in range(args.warmup):
+            graphs[w_ % copies].replay()
+
+        def run(i):
+            graphs[i % copies].replay()
     except Exception as exc:  # a collective that cannot be captured on this stack: time the eager loop
         print(f"[bench] graph capture failed ({type(exc).__name__}: {exc}); timing the eager loop", file=sys.stderr)
         timed_as = "eager"
-        run = step
+
+        def run(i):
+            step(i % copies)
     with ClockSampler(local_rank) as clocks:
         ms_total = timed(run, args.steps)
     ms_step = ms_total / args.steps
     value = flops_per_step() / (ms_step * 1e-3) / 1e12
+
+    # ---- parity of what the timed loop produced: every SpMM's gathered output against the fp32 host GEMM on
+    # sampled rows of the full (unsharded) weight, at every world size
+    def full_output(k):
+        if world == 1:
+            return outs[k]
+        if exchange == "peer":
+            return peer[k].bufs[0]
+        return gathered[k].permute(1, 0, 2).reshape(k[1], -1)
+
+    torch.cuda.synchronize()
+    parity = None
+    if rank == 0:
+        import oracle
+        oracle.set_num_threads(host_threads())
+        worst, rows_checked = 0.0, 0
+        for i, (M, K) in enumerate(SHAPES):
+            rows = np.unique(np.linspace(0, M - 1, num=min(M, 768)).astype(np.int64))
+            A_rows = gen_weight(M, K, i, dev)[torch.from_numpy(rows).to(dev)].cpu().numpy()
+            for N in NS:
+                ref = oracle.gemm_f32(A_rows, acts[(i, N)].cpu().numpy())            # [N, rows]
+                got = full_output((i, N))[:, torch.from_numpy(rows).to(dev)].float().cpu().numpy()
+                worst = max(worst, float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-12)))
+            rows_checked += len(rows)
+        parity = {"max_rel_err": worst, "ok": bool(worst <= REL_TOL), "tolerance": REL_TOL,
+                  "rows_checked_per_step": rows_checked, "against": "fp32 host GEMM (oracle) on sampled rows of every SpMM"}
 
     # ---- end to end through the C ABI with host buffers: activations in, outputs back, every SpMM
     h_acts = {k: v.cpu().pin_memory() for k, v in acts.items()}
     h_outs = {k: torch.empty((k[1], SHAPES[k[0]][0]), dtype=torch.float16).pin_memory() for k in acts}
     d_full = {k: torch.empty((k[1], SHAPES[k[0]][0]), dtype=torch.float16, device=dev) for k in acts}
 
-    def e2e_step():
+    def e2e_step(it):
+        c = it % copies
         for k in order:
             i, N = k
             acts[k].copy_(h_acts[k], non_blocking=True)
-            sp.spmm(mats[i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
+            sp.spmm(mat_sets[c][i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
             if world > 1:
                 dist.all_gather_into_tensor(gathered[k], outs[k])
                 d_full[k].copy_(gathered[k].permute(1, 0, 2).reshape(N, -1))
@@ -320,8 +451,8 @@ def main():
                 h_outs[k].copy_(outs[k], non_blocking=True)
         torch.cuda.synchronize()
 
-    for _ in range(3):
-        e2e_step()
+    for it in range(3):
+        e2e_step(it)
     e2e_ms = timed(e2e_step, args.steps) / args.steps
     h2d = sum(N * SHAPES[i][1] * 2 for (i, N) in order)
     d2h = sum(N * SHAPES[i][0] * 2 for (i, N) in order)
@@ -334,6 +465,13 @@ def main():
 
     peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes_step / (ms_step * 1e-3) / 1e9
+    if rotating:
+        l2_note = (f"rotating: {copies} cop{'y' if copies == 1 else 'ies'} of {weight_bytes / 1e6:.0f} MB of compressed weights "
+                   f"per rank are streamed between two uses of the same bytes (L2: {l2_bytes / 1e6:.0f} MB)")
+    else:
+        l2_note = (f"L2-warm: {copies * weight_bytes / 1e6:.0f} MB of compressed weights per rank against an L2 of "
+                   f"{l2_bytes / 1e6:.0f} MB")
+    ratio, capture = traffic_ratio()
     line = {
         "metric": "spmm_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
@@ -342,8 +480,7 @@ def main():
                    "split_k": {f"{SHAPES[i][0]}x{SHAPES[i][1]}xN{N}": splits[(i, N)] for (i, N) in order},
                    "schedule": args.schedule,
                    "parallelism": f"tp{world}_m_split_allgather_{exchange}" if world > 1 else "single_gpu",
-                   "l2": f"inputs larger than L2: {weight_bytes / 1e6:.0f} MB of compressed weights per rank "
-                         "rotate between reuses"},
+                   "l2": l2_note, "weight_copies": copies},
         "hbm_gbs": achieved * world if world > 1 else achieved,
         "e2e": {"value": flops_per_step() / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
@@ -352,33 +489,65 @@ def main():
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks.summary(),
         "device_status": status,
+        "parity": parity,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": None,
+                     "peak_kind": peak_kind, "traffic": ratio * alg_bytes_step / len(order) if ratio else None,
                      "note": "algorithmic bytes of this rank's SpMMs / event time of the step (SpMM kernel plus "
-                             "its split-K reduction launch)"},
+                             "its split-K reduction launch); traffic = average algorithmic bytes of a launch x the "
+                             "dram-bytes / algorithmic-bytes ratio of the capture named in traffic_from",
+                     "traffic_from": capture},
     }
-    # DRAM traffic of one SpMM launch: the ncu capture of the kernel (profiles/) shows
-    # dram__bytes_read + dram__bytes_write = 1.024 x the algorithmic bytes (191.98 + 5.37 MB against 192.7 MB);
-    # traffic grows with the bytes streamed, so the average launch of this workload is scaled by that ratio.
-    line["roofline"]["traffic"] = 1.024 * alg_bytes_step / len(order)
-    if world == 1:
+    if shard_check is not None:
+        line["shard_encoding_bit_exact"] = shard_check
+    if exchange_probe:
+        line["exchange_probe_ms_per_step"] = exchange_probe
+    if world == 1 and not args.no_extras:
         line["comparators"] = {"cublas_dense_fp16": cublas_dense(dev, acts, order, args)}
-    if world == 1 and not args.case:
-        line["cpu_baseline"] = cpu_baseline(mats)
+        rs = ref_style(dev, sp, mats, acts, order, args)
+        if rs is not None:
+            line["comparators"]["reference_style_mma_sync"] = rs
+        line["l2_hot"] = l2_hot(dev, sp, mats, acts, outs, ws, splits, order, ms_step)
+    if world == 1 and not args.case and not args.no_extras:
+        line["cpu_baseline"] = cpu_baseline()
         line["encoder"] = encoder_timing(dev)
     print(json.dumps(line), flush=True)
+    failed = (parity is not None and not parity["ok"]) or shard_check is False or status != 0
     if world > 1:
-        finish_ranks(dist)
+        finish_ranks(dist, 1 if failed else 0)
+    if failed:
+        sys.exit(1)
 
 
-def finish_ranks(dist):
+def finish_ranks(dist, code=0):
     """All ranks meet, then leave without tearing the communicator down: destroying a process group while a
     captured graph still holds its collectives did not return on this stack."""
     dist.barrier()
     torch.cuda.synchronize()
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0)
+    os._exit(code)
+
+
+def graph_time(fn, args):
+    """fn() captured into a CUDA graph on a side stream, replayed: ms per replay."""
+    work = torch.cuda.Stream()
+    with torch.cuda.stream(work):
+        for _ in range(args.warmup):
+            fn()
+    work.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=work):
+        fn()
+    for _ in range(args.warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / args.steps
 
 
 def cublas_dense(dev, acts, order, args):
@@ -391,32 +560,77 @@ def cublas_dense(dev, acts, order, args):
         for k in order:
             torch.mm(acts[k], dense[k[0]].t(), out=outs[k])
 
-    work = torch.cuda.Stream()
-    with torch.cuda.stream(work):
-        for _ in range(args.warmup):
-            step()
-    work.synchronize()
-    graph = torch.cuda.CUDAGraph()   # timed like the SpMM loop: one captured step, replayed
-    with torch.cuda.graph(graph, stream=work):
-        step()
-    for _ in range(args.warmup):
-        graph.replay()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = graph_time(step, args)
     dense_bytes = sum(2 * SHAPES[i][0] * SHAPES[i][1] for (i, N) in order)
     return {"value": flops_per_step() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
             "dense_weight_gbs": dense_bytes / (ms * 1e-3) / 1e9}
 
 
-def cpu_baseline(mats):
+def ref_style(dev, sp, mats, acts, order, args):
+    """The reference's mma.sync / cp.async kernel (oracle/_ref/libref_style_spmm.so, put together from the reference's
+    own device functions and compiled for sm_100a) on the same encoded weights, same rotation, timed the same way.
+    Split_K from the reference's per-M table where it has an entry, else 1."""
+    import oracle
+    if not oracle.have_ref_style():
+        return None
+    ok_ns = [N for N in NS if N in (8, 16, 32, 64) or N % 128 == 0]
+    if len(ok_ns) != len(NS):
+        return {"unavailable": "the reference kernel only takes N in {8, 16, 32, 64, k*128}"}
+    bufs = {}
+    for (i, N) in order:
+        W = mats[i]
+        sk = REF_SPLIT_K.get(W.M, 1)
+        if sk > 1 and (W.M * N) % 256:
+            sk = 1
+        B = acts[(i, N)]
+        if N == 8:   # that kernel copies a 16-row activation tile
+            Bp = torch.zeros((16, B.shape[1]), dtype=B.dtype, device=dev)
+            Bp[:8] = B
+            B = Bp
+        bufs[(i, N)] = (B, torch.empty((N, W.M), dtype=torch.float16, device=dev),
+                        torch.empty(max(sk, 1) * N * W.M, dtype=torch.float16, device=dev), sk, int(W.max_nnz.item()))
+
+    def step():
+        s = torch.cuda.current_stream().cuda_stream
+        for (i, N) in order:
+            W = mats[i]
+            B, C, w, sk, mx = bufs[(i, N)]
+            oracle.ref_style_spmm(s, W.vals.data_ptr(), W.gtile.data_ptr(), W.mtile.data_ptr(), W.bitmap.data_ptr(),
+                                  B.data_ptr(), C.data_ptr(), W.M, N, W.K, w.data_ptr(), sk, mx)
+
+    try:
+        ms = graph_time(step, args)
+    except Exception as exc:
+        return {"unavailable": f"{type(exc).__name__}: {exc}"}
+    alg = sum(mats[i].algorithmic_bytes(N) for (i, N) in order)
+    return {"value": flops_per_step() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+            "hbm_gbs": alg / (ms * 1e-3) / 1e9,
+            "split_k": {f"{SHAPES[i][0]}x{SHAPES[i][1]}xN{N}": bufs[(i, N)][3] for (i, N) in order}}
+
+
+def l2_hot(dev, sp, mats, acts, outs, ws, splits, order, cold_ms):
+    """The same SpMMs with each one launched five times in a row: the four repeats find what fits of their weight
+    in L2.  Reported as the time of a step made of such repeats, beside the rotating (cold) figure."""
+    class A:
+        warmup, steps = 3, 10
+
+    def once(rep):
+        def fn():
+            for k in order:
+                for _ in range(rep):
+                    sp.spmm(mats[k[0]], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
+        return fn
+
+    t1, t5 = graph_time(once(1), A), graph_time(once(5), A)
+    hot = (t5 - t1) / 4.0
+    return {"ms_per_step": hot, "value": flops_per_step() / (hot * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "cold_ms_per_step": cold_ms}
+
+
+def cpu_baseline():
     """fp32 host GEMM over the decoded weight (the CPU restatement of the path), all host threads, bounded sample."""
     import oracle
+    cores = oracle.set_num_threads(host_threads())
     M, K = SHAPES[1]
     A = gen_weight(M, K, 1, "cpu").numpy()
     enc = oracle.encode(A)
@@ -430,7 +644,7 @@ def cpu_baseline(mats):
         reps += 1
     dt = (time.perf_counter() - t0) / reps
     flops = sum(2.0 * M * K * N for N in NS)
-    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
             "sample": f"out-proj matrix {M}x{K} at N={NS}, {reps} passes in {dt * reps:.1f} s"}
 
 

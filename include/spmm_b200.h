@@ -85,6 +85,20 @@ void Our_GenSparseMatrixBinFile(char* DenseMatrixFileName, int M, int K, char* C
 int spb_gen_bin_files(const char* dense, int M, int K, const char* val, const char* gtile, const char* mtile,
                       const char* bitmap, const char* max_nnz, const char* sizes);
 
+/*
+ * Loader of the six files Our_GenSparseMatrixBinFile writes (csrc/SpMM_API.cuh:288-319), the counterpart of
+ * what FasterTransformer's patched weight loader does with them (third_party/ft_spinfer.patch:2336-2357:
+ * loadDataArrayFromBin of .NZWeights, .gtile, .mtile, .ltile and .intile into device buffers whose sizes come
+ * from the per-rank list files).  Pure host code.  `sizes` is the .OutputSizes file; it is checked against M and K
+ * ([val_count, G+1, 4G, 64G]).  On success the four arrays are malloc()ed and owned by the caller (free() or
+ * spb_free_host): vals val_count halves, gtile G+1 ints, mtile 4G ints, bitmap 64G uint64; *max_nnz_out is the
+ * content of the .intile file (the largest padded tile count, rounded up to a multiple of 64 by the writer).
+ * Returns 0, or cudaErrorInvalidValue when a file is missing, short or inconsistent (message in spb_last_error).
+ */
+int spb_load_bin_files(const char* val, const char* gtile, const char* mtile, const char* bitmap, const char* max_nnz,
+                       const char* sizes, int M, int K, uint16_t** vals_out, int** mtile_out, int** gtile_out,
+                       uint64_t** bitmap_out, int* max_nnz_out, int* val_count_out);
+
 /* --------------------------------------------------------------------- SpMM */
 
 /*

@@ -12,6 +12,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_HERE, "liboracle.so")
 _REF = os.path.join(_HERE, "_ref", "libref_encoder.so")
+_REF_SPMM = os.path.join(_HERE, "_ref", "libref_style_spmm.so")
 
 _u16p = ctypes.POINTER(ctypes.c_uint16)
 _i32p = ctypes.POINTER(ctypes.c_int)
@@ -23,8 +24,21 @@ def build(force=False):
     """Compile liboracle.so (and _ref/ when the reference sources are present)."""
     if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(os.path.join(_HERE, "oracle.c")):
         subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, capture_output=True)
-    if os.path.isdir("/root/reference/csrc") and (force or not os.path.exists(_REF)):
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+    # REF_DIR (the csrc directory of a checkout of the reference) overrides the Makefile's default
+    ref_dir = os.environ.get("REF_DIR") or _makefile_ref_dir()
+    if ref_dir and os.path.isdir(ref_dir) and (force or not os.path.exists(_REF) or not os.path.exists(_REF_SPMM)):
+        subprocess.run(["make", "-C", _HERE, "ref", f"REF_DIR={ref_dir}"], check=True, capture_output=True)
+
+
+def _makefile_ref_dir():
+    """Default of REF_DIR in the Makefile beside this file."""
+    try:
+        for line in open(os.path.join(_HERE, "Makefile")):
+            if line.startswith("REF_DIR ?="):
+                return line.split("=", 1)[1].strip()
+    except OSError:
+        pass
+    return None
 
 
 def _p(a, t):
@@ -61,6 +75,28 @@ def ref():
         _ref.ref_encode_bitmap_v3.restype = ctypes.c_int
         _ref.ref_free.argtypes = [ctypes.c_void_p]
     return _ref
+
+
+def have_ref_style():
+    return os.path.exists(_REF_SPMM)
+
+
+_ref_spmm = None
+
+
+def ref_style_spmm(stream, vals, gtile, mtile, bitmap, B, C, M, N, K, workspace, split_k, max_nnz):
+    """The reference-style mma.sync / cp.async SpMM (oracle/ref_style_spmm.cu, built from the reference's device
+    functions) on device pointers given as integers.  A GPU comparator and numerics pin for tests and bench.py.
+    N in {8, 16, 32, 64, k*128}; for N = 8 the buffer behind B must be readable for 16 rows."""
+    global _ref_spmm
+    if _ref_spmm is None:
+        _ref_spmm = ctypes.CDLL(_REF_SPMM)
+        _ref_spmm.ref_style_spmm.restype = ctypes.c_int
+        _ref_spmm.ref_style_spmm.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int,
+                                                                                      ctypes.c_int]
+    rc = _ref_spmm.ref_style_spmm(stream, vals, gtile, mtile, bitmap, B, C, M, N, K, workspace, split_k, max_nnz)
+    if rc != 0:
+        raise RuntimeError(f"ref_style_spmm failed: cudaError {rc}")
 
 
 def _as_u16(a):
@@ -130,6 +166,19 @@ def ref_encode(A):
     return out
 
 
+def ref_gen_bin_files(dense_path, M, K, prefix):
+    """The reference's own Our_GenSparseMatrixBinFile (compiled into oracle/_ref) on `dense_path`; writes the six
+    files `prefix`.{NZWeights,gtile,mtile,ltile,intile,OutputSizes}.bin.  The reference prints a summary line and
+    calls exit(-1) on I/O errors, so only call it with files that exist."""
+    r = ref()
+    names = [prefix + sfx for sfx in (".NZWeights.bin", ".gtile.bin", ".mtile.bin", ".ltile.bin", ".intile.bin",
+                                      ".OutputSizes.bin")]
+    r.ref_gen_bin_files.restype = None
+    r.ref_gen_bin_files.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_char_p] * 6
+    r.ref_gen_bin_files(dense_path.encode(), M, K, *[n.encode() for n in names])
+    return names
+
+
 def decode(enc):
     A = np.empty((enc.M, enc.K), np.uint16)
     vals = enc.vals if enc.vals.size else np.zeros(1, np.uint16)
@@ -184,3 +233,9 @@ def total_error(a, b):
 
 def num_threads():
     return lib().oracle_num_threads()
+
+
+def set_num_threads(n):
+    """Threads for the OpenMP loops of the oracle from now on (see oracle_set_num_threads)."""
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()

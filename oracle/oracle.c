@@ -311,6 +311,17 @@ double oracle_total_error(const uint16_t *a, const uint16_t *b, size_t n)
     return e;
 }
 
+/* Number of OpenMP threads the GEMMs of this file use from now on (a launcher may have exported
+ * OMP_NUM_THREADS=1 for its children; the timed CPU baseline wants all cores of the box). */
+void oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void)
 {
 #ifdef _OPENMP

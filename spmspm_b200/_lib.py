@@ -27,6 +27,8 @@ SIGNATURES = {
                                          _vp, _vp, _vp, _vp]),
     "Our_GenSparseMatrixBinFile": (None, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_char_p] * 6),
     "spb_gen_bin_files": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int] + [ctypes.c_char_p] * 6),
+    "spb_load_bin_files": (ctypes.c_int, [ctypes.c_char_p] * 6 + [ctypes.c_int, ctypes.c_int, ctypes.POINTER(_u16p),
+                                          ctypes.POINTER(_i32p), ctypes.POINTER(_i32p), ctypes.POINTER(_u64p), _i32p, _i32p]),
     "spb_spmm_bitmap_v3": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,
                                           ctypes.c_int, _vp, ctypes.c_int]),
     "spb_spmm_bitmap_v3_noalloc": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,

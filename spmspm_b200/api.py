@@ -94,6 +94,76 @@ def our_gen_sparse_matrix_bin_file(dense, M, K, val, gtile, mtile, bitmap, max_n
         raise SpmmError(_lib.last_error())
 
 
+# --------------------------------------------------------------------------- on-disk format
+
+BIN_SUFFIXES = (".NZWeights.bin", ".gtile.bin", ".mtile.bin", ".ltile.bin", ".intile.bin", ".OutputSizes.bin")
+
+
+def bin_file_names(prefix):
+    """The six file names the reference's converter derives from a dense weight file `prefix`.bin
+    (end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:70-76), in the argument order of
+    Our_GenSparseMatrixBinFile: values, global offsets, median offsets, bitmaps, max_nnz, sizes."""
+    return tuple(prefix + sfx for sfx in BIN_SUFFIXES)
+
+
+def load_bin_files(prefix, M, K):
+    """Read the six files of one weight matrix (spb_load_bin_files) into a HostEncoded.
+
+    The per-8x8-tile counts are not part of the on-disk format (csrc/SpMM_API.cuh:288-319 writes five arrays
+    and the sizes); tile_nnz is rebuilt from the bitmaps."""
+    names = [n.encode() for n in bin_file_names(prefix)]
+    lib = _lib.load()
+    u16p, i32p, u64p = ctypes.POINTER(ctypes.c_uint16), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_uint64)
+    vals, mt, gt, bm = u16p(), i32p(), i32p(), u64p()
+    mx, n = ctypes.c_int(0), ctypes.c_int(0)
+    rc = lib.spb_load_bin_files(*names, M, K, ctypes.byref(vals), ctypes.byref(mt), ctypes.byref(gt), ctypes.byref(bm),
+                                ctypes.byref(mx), ctypes.byref(n))
+    if rc != 0:
+        raise SpmmError(f"load_bin_files({prefix}) failed: {_lib.last_error()}")
+    try:
+        G = (M // 64) * (K // 64)
+        bitmap = np.ctypeslib.as_array(bm, (64 * G,)).copy()
+        bits = np.unpackbits(bitmap.view(np.uint8)).reshape(-1, 64).sum(axis=1).astype(np.int32)
+        out = HostEncoded(M, K,
+                          np.ctypeslib.as_array(vals, (n.value,)).copy() if n.value else np.zeros(0, np.uint16),
+                          bits, np.ctypeslib.as_array(mt, (4 * G,)).copy(),
+                          np.ctypeslib.as_array(gt, (G + 1,)).copy(), bitmap, mx.value)
+    finally:
+        for p in (vals, mt, gt, bm):
+            lib.spb_free_host(ctypes.cast(p, ctypes.c_void_p))
+    return out
+
+
+RANK_LISTS = ("val_count_List", "num_gtiles_List", "num_mtiles_List", "num_ltiles_List", "SplitK_List")
+
+
+def write_rank_lists(directory, rank, prefixes, split_ks):
+    """The five per-rank list files FasterTransformer's loader reads before it allocates the weight buffers
+    (third_party/ft_spinfer.patch:3133-3147): one int32 per weight matrix, in `prefixes` order, taken from each
+    matrix's .OutputSizes file as the reference's converter does (huggingface_opt_convert_Phase2.py:329-360);
+    a matrix that was left dense (no .OutputSizes file) gets zeros and Split_K 0."""
+    import os
+    rows = []
+    for prefix, sk in zip(prefixes, split_ks):
+        f = prefix + ".OutputSizes.bin"
+        if os.path.exists(f):
+            sz = np.fromfile(f, dtype=np.int32)
+            if sz.shape[0] != 4:
+                raise SpmmError(f"{f} must hold four int32")
+            rows.append([int(sz[0]), int(sz[1]), int(sz[2]), int(sz[3]), int(sk)])
+        else:
+            rows.append([0, 0, 0, 0, 0])
+    arr = np.asarray(rows, dtype=np.int32).reshape(-1, 5)
+    for col, name in enumerate(RANK_LISTS):
+        arr[:, col].copy().tofile(os.path.join(directory, f"{name}.{rank}.bin"))
+
+
+def read_rank_lists(directory, rank):
+    """Inverse of write_rank_lists: dict name -> int32 array (one entry per weight matrix)."""
+    import os
+    return {name: np.fromfile(os.path.join(directory, f"{name}.{rank}.bin"), dtype=np.int32) for name in RANK_LISTS}
+
+
 # --------------------------------------------------------------------------- encoder (device)
 
 @dataclass

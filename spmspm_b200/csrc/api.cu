@@ -46,30 +46,52 @@ cudaError_t device_status_ptr(int** out)
     return cudaSuccess;
 }
 
-static bool aligned16(const void* p)
+bool aligned16(const void* p)
 {
     return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+// Shape, null and alignment checks shared by every SpMM entry point: the kernel hands Compressed_A, the median
+// offsets and the bitmaps to bulk copies and B to a tensor map, all of which fault on the device when a pointer
+// is not 16-byte aligned, so a bad pointer must be turned into an error code here and nothing launched.
+cudaError_t check_spmm_args(const char* who, const void* vals, const void* gtile, const void* mtile, const void* bitmap,
+                            const void* max_nnz, const void* B, int M, int N, int K, const void* ws, int split_k)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || (M % 64) || (K % 64)) {
+        set_error("%s: M and K must be positive multiples of 64, N positive (M=%d N=%d K=%d)", who, M, N, K);
+        return cudaErrorInvalidValue;
+    }
+    if (split_k < 1 || split_k > K / 64) {
+        set_error("%s: Split_K=%d out of range 1..%d", who, split_k, K / 64);
+        return cudaErrorInvalidValue;
+    }
+    if (!vals || !gtile || !mtile || !bitmap || !max_nnz || !B || (split_k > 1 && !ws)) {
+        set_error("%s: null device pointer", who);
+        return cudaErrorInvalidValue;
+    }
+    if (!aligned16(vals) || !aligned16(mtile) || !aligned16(bitmap) || !aligned16(B) || (split_k > 1 && !aligned16(ws))) {
+        set_error("%s: Compressed_A, TileOffsets_Median, bitmap, B and the workspace must be 16-byte aligned", who);
+        return cudaErrorMisalignedAddress;
+    }
+    if (reinterpret_cast<uintptr_t>(gtile) & 3u) {
+        set_error("%s: TileOffsets must be 4-byte aligned", who);
+        return cudaErrorMisalignedAddress;
+    }
+    return cudaSuccess;
 }
 
 static cudaError_t spmm_checked(cudaStream_t stream, const uint16_t* vals, const int* gtile, const int* mtile,
                                 const uint64_t* bitmap, const int* max_nnz, const uint16_t* B, uint16_t* C, int M,
                                 int N, int K, uint16_t* ws, int split_k)
 {
-    if (M <= 0 || N <= 0 || K <= 0 || (M % 64) || (K % 64)) {
-        set_error("SpMM: M and K must be positive multiples of 64, N positive (M=%d N=%d K=%d)", M, N, K);
-        return cudaErrorInvalidValue;
-    }
-    if (split_k < 1 || split_k > K / 64) {
-        set_error("SpMM: Split_K=%d out of range 1..%d", split_k, K / 64);
-        return cudaErrorInvalidValue;
-    }
-    if (!vals || !gtile || !mtile || !bitmap || !max_nnz || !B || !C || (split_k > 1 && !ws)) {
+    cudaError_t chk = check_spmm_args("SpMM", vals, gtile, mtile, bitmap, max_nnz, B, M, N, K, ws, split_k);
+    if (chk != cudaSuccess) return chk;
+    if (!C) {
         set_error("SpMM: null device pointer");
         return cudaErrorInvalidValue;
     }
-    if (!aligned16(vals) || !aligned16(mtile) || !aligned16(bitmap) || !aligned16(B) || !aligned16(C) ||
-        (split_k > 1 && !aligned16(ws))) {
-        set_error("SpMM: Compressed_A, TileOffsets_Median, bitmap, B, C and the workspace must be 16-byte aligned");
+    if (!aligned16(C)) {
+        set_error("SpMM: C must be 16-byte aligned");
         return cudaErrorMisalignedAddress;
     }
     SpmmArgs a;
@@ -231,6 +253,73 @@ static int gen_bin_files_impl(const char* dense, int M, int K, const char* valf,
     return rc;
 }
 
+// Reads `count` items of `size` bytes from a file that must hold at least that many (the check
+// FasterTransformer's loader makes, third_party/ft_spinfer.patch:4773-4810).
+static bool read_exact(const char* path, void* dst, size_t size, size_t count, const char* what)
+{
+    std::ifstream in(path, std::ios::in | std::ios::binary);
+    if (!in.is_open()) {
+        set_error("load: file %s (%s) cannot be opened", path, what);
+        return false;
+    }
+    in.read((char*)dst, (std::streamsize)(size * count));
+    if ((size_t)in.gcount() != size * count) {
+        set_error("load: file %s (%s) holds %ld bytes, %ld needed", path, what, (long)in.gcount(), (long)(size * count));
+        return false;
+    }
+    return true;
+}
+
+static int load_bin_files_impl(const char* valf, const char* gtf, const char* mtf, const char* bmf, const char* mxf,
+                               const char* szf, int M, int K, uint16_t** vals, int** mtile, int** gtile,
+                               uint64_t** bitmap, int* max_nnz, int* val_count)
+{
+    *vals = nullptr;
+    *mtile = *gtile = nullptr;
+    *bitmap = nullptr;
+    if (M <= 0 || K <= 0 || (M % 64) || (K % 64)) {
+        set_error("load: M and K must be positive multiples of 64 (M=%d K=%d)", M, K);
+        return (int)cudaErrorInvalidValue;
+    }
+    const long long G = (long long)(M / 64) * (K / 64);
+    int sizes[4] = {0, 0, 0, 0};  // [val_count, G+1, 4G, 64G] (reference csrc/SpMM_API.cuh:304-308)
+    if (!read_exact(szf, sizes, 4, 4, "OutputSizes")) return (int)cudaErrorInvalidValue;
+    if (sizes[0] < 0 || sizes[1] != G + 1 || sizes[2] != 4 * G || sizes[3] != 64 * G) {
+        set_error("load: %s says [%d, %d, %d, %d], a %d x %d matrix needs [n, %lld, %lld, %lld]", szf, sizes[0], sizes[1],
+                  sizes[2], sizes[3], M, K, G + 1, 4 * G, 64 * G);
+        return (int)cudaErrorInvalidValue;
+    }
+    const size_t n = (size_t)sizes[0];
+    uint16_t* v = (uint16_t*)malloc(n ? n * 2 : 16);
+    int* gt = (int*)malloc((size_t)(G + 1) * 4);
+    int* mt = (int*)malloc((size_t)G * 16);
+    uint64_t* bm = (uint64_t*)malloc((size_t)G * 512);
+    int mx = 0;
+    bool ok = v && gt && mt && bm;
+    if (!ok) set_error("load: out of host memory");
+    ok = ok && (n == 0 || read_exact(valf, v, 2, n, "NZWeights")) && read_exact(gtf, gt, 4, (size_t)(G + 1), "gtile") &&
+         read_exact(mtf, mt, 4, (size_t)(4 * G), "mtile") && read_exact(bmf, bm, 8, (size_t)(64 * G), "ltile") &&
+         read_exact(mxf, &mx, 4, 1, "intile");
+    if (ok && (gt[0] != 0 || (size_t)gt[G] != n)) {
+        set_error("load: global tile offsets run from %d to %d, the value file holds %ld", gt[0], gt[G], (long)n);
+        ok = false;
+    }
+    if (!ok) {
+        free(v);
+        free(gt);
+        free(mt);
+        free(bm);
+        return (int)cudaErrorInvalidValue;
+    }
+    *vals = v;
+    *gtile = gt;
+    *mtile = mt;
+    *bitmap = bm;
+    *max_nnz = mx;
+    *val_count = (int)n;
+    return 0;
+}
+
 }  // namespace spb
 
 // ================================================================ extern "C" entry points
@@ -287,6 +376,19 @@ int spb_gen_bin_files(const char* dense, int M, int K, const char* val, const ch
                       const char* bitmap, const char* max_nnz, const char* sizes)
 {
     return spb::gen_bin_files_impl(dense, M, K, val, gtile, mtile, bitmap, max_nnz, sizes, false);
+}
+
+int spb_load_bin_files(const char* val, const char* gtile, const char* mtile, const char* bitmap, const char* max_nnz,
+                       const char* sizes, int M, int K, uint16_t** vals_out, int** mtile_out, int** gtile_out,
+                       uint64_t** bitmap_out, int* max_nnz_out, int* val_count_out)
+{
+    if (!val || !gtile || !mtile || !bitmap || !max_nnz || !sizes || !vals_out || !mtile_out || !gtile_out ||
+        !bitmap_out || !max_nnz_out || !val_count_out) {
+        spb::set_error("load: null argument");
+        return (int)cudaErrorInvalidValue;
+    }
+    return spb::load_bin_files_impl(val, gtile, mtile, bitmap, max_nnz, sizes, M, K, vals_out, mtile_out, gtile_out,
+                                    bitmap_out, max_nnz_out, val_count_out);
 }
 
 int spb_spmm_bitmap_v3(void* stream, const uint16_t* A, const uint16_t* Compressed_A, const int* TileOffsets,

@@ -63,5 +63,9 @@ void pop_static_schedule();
 cudaError_t reset_schedule_scratch();  // clears the arrival counters of the current device
 
 void set_error(const char* fmt, ...);
+bool aligned16(const void* p);
+// Argument checks of the SpMM entry points (api.cu): cudaSuccess, or an error code with the message set.
+cudaError_t check_spmm_args(const char* who, const void* vals, const void* gtile, const void* mtile, const void* bitmap,
+                            const void* max_nnz, const void* B, int M, int N, int K, const void* ws, int split_k);
 
 }  // namespace spb

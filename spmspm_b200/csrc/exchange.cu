@@ -116,9 +116,11 @@ extern "C" int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compre
                        M_shard, K_Global, M_full, row_offset);
         return (int)cudaErrorInvalidValue;
     }
-    if (!Compressed_A || !TileOffsets || !TileOffsets_Median || !bitmap || !max_nnz_intile || !B) {
-        spb::set_error("spb_spmm_bitmap_v3_allgather: null device pointer");
-        return (int)cudaErrorInvalidValue;
+    {
+        const cudaError_t chk = spb::check_spmm_args("spb_spmm_bitmap_v3_allgather", Compressed_A, TileOffsets, TileOffsets_Median,
+                                                     bitmap, max_nnz_intile, B, M_shard, N_Global, K_Global, Reduction_Workspace,
+                                                     Split_K);
+        if (chk != cudaSuccess) return (int)chk;
     }
     spb::SpmmArgs a;
     a.vals = Compressed_A;
@@ -131,12 +133,6 @@ extern "C" int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compre
     a.M = M_shard;
     a.N = N_Global;
     a.K = K_Global;
-    if (Split_K < 1 || Split_K > K_Global / 64 || (Split_K > 1 && (!Reduction_Workspace ||
-                                                                  (reinterpret_cast<uintptr_t>(Reduction_Workspace) & 15u)))) {
-        spb::set_error("spb_spmm_bitmap_v3_allgather: Split_K=%d needs 1..%d and, above 1, an aligned workspace", Split_K,
-                       K_Global / 64);
-        return (int)cudaErrorInvalidValue;
-    }
     a.split_k = Split_K;
     a.wait_flags = B_flags;
     a.wait_n = n_peers;

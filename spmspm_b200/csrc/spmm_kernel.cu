@@ -37,26 +37,15 @@
 #include <atomic>
 #include <mutex>
 
-#ifndef SPB_PROBE
-#define SPB_PROBE 0
-#endif
-#ifndef SPB_PROBE_MMAS
-#define SPB_PROBE_MMAS 4  // timing probes only: fewer MMAs per k-tile (wrong results)
-#endif
-#ifndef SPB_PROBE_SKIP
-#define SPB_PROBE_SKIP 0  // timing probes only: copies left out (1 activations, 2 bitmaps and median offsets, 4 values)
-#endif
-#ifndef SPB_PROBE_WAIT
-#define SPB_PROBE_WAIT 0
-#endif
 #ifndef SPB_PROF
 #define SPB_PROF 0  // development only: per-phase clock sums of one decode warp, the MMA warp and a producer warp
 #endif
-#ifndef SPB_SEG3
-#define SPB_SEG3 1  // row segments driven by a per-tile table entry (bitmap half + start of the half's values) and a byte-indexed selector table
+#ifndef SPB_IMAD
+#define SPB_IMAD 1
 #endif
-#ifndef SPB_PROBE_SEGS
-#define SPB_PROBE_SEGS 8  // timing probes only: fewer row segments per k-tile (wrong results)
+#ifndef SPB_UNIT
+#define SPB_UNIT 1  // k-tiles a decode group expands per turn (2 measured 3 % slower: the decode warps are bound by
+                    // instruction issue, so paying the chain of waits once per two k-tiles buys nothing)
 #endif
 namespace spb {
 #if SPB_PROF
@@ -83,7 +72,9 @@ constexpr int kKT = 4;
 constexpr int kDecodeGroups = SPB_GROUPS;
 static_assert(kDecodeGroups >= kKT && kDecodeGroups <= 6, "a stage must not give a group two k-tiles; 32 warps at most");
 // A operand blocks in tensor memory (32 columns = one k-tile each), used in turn: k-tile t uses block t % kABlocks.
-constexpr int kABlocks = 8;
+// With the accumulators kept to 128 columns there is room for 12: a group that expands kUnit k-tiles per turn can
+// start its next turn while the tensor core still reads the blocks of its last one.
+constexpr int kABlocks = 12;
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
@@ -109,13 +100,9 @@ constexpr int kMaxStages = 24;
 //                {bitmap rows 0-3, address of the first value of rows 0-3, bitmap rows 4-7, address of the first value of rows 4-7}
 //   selector table  indexed by a row's 8-bit mask: {low-nibble entry, high-nibble entry} (see lut_low_entry), 16 copies
 //                interleaved so that the 16 lanes of a half warp always read 16 different 8-byte slots
-#if SPB_SEG3
-constexpr int kTileTabBytes = 512;
+constexpr int kUnit = SPB_UNIT;
+constexpr int kTileTabBytes = 512 * kUnit;
 constexpr int kLutBytes = 256 * 16 * 8;
-#else
-constexpr int kTileTabBytes = 128;
-constexpr int kLutBytes = 0;
-#endif
 constexpr int kHeaderBytes = 1024 + kTileTabBytes * 4 * kDecodeGroups + kLutBytes;
 static_assert(kHeaderBytes % 1024 == 0, "the stages behind the header must stay 1024-byte aligned");
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -200,9 +187,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // integer-pipe cycles from the decode warps of the same scheduler.
 __device__ __forceinline__ bool mbar_wait_patient(uint32_t bar, uint32_t parity, volatile int* abort_flag)
 {
-#if SPB_PROBE_WAIT
-    return mbar_wait(bar, parity, abort_flag);
-#endif
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (i >= 4) {
@@ -466,6 +450,13 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
+// a * b + c on the multiply-add pipe (the compiler turns a * 2 + c written in C++ into integer-ALU shifts and adds)
+__device__ __forceinline__ uint32_t imad(uint32_t a, uint32_t b, uint32_t c)
+{
+    uint32_t d;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 __device__ __forceinline__ void tc_st_32x32b_x8(uint32_t taddr, const uint32_t* r)
 {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
@@ -540,42 +531,28 @@ __device__ __forceinline__ void lds32x3_before(uint32_t addr, uint32_t& a, uint3
                  : "=&r"(a), "=&r"(b), "=&r"(c)
                  : "r"(addr));
 }
-// Load half for one row segment.  lo, hi: the 64-bit bitmap of the segment's tile; tile: shared address of
-// the tile's first value.
-//   below_lo/below_hi  thread constants: bitmap bits of the tile rows above this thread's row
-//   rsel               permute selector moving this row's mask byte to byte 0
-__device__ __forceinline__ void unit_load(uint32_t lo, uint32_t hi, uint32_t tile, uint32_t below_lo,
-                                          uint32_t below_hi, uint32_t rsel, uint32_t lut, UnitLoads& u)
-{
-    const uint32_t w0 = tile + 2u * (__popc(lo & below_lo) + __popc(hi & below_hi));
-    const uint32_t g = prmt(lo, hi, rsel);                 // row mask in byte 0 (bytes 1-3 are not clean)
-    const uint32_t wt = w0 + 2u * __popc(g & 0xffu);       // address just past the row's last value
-    lds32x3(w0 & ~3u, u.x0, u.x1, u.x2);
-    lds32x3_before(wt & ~3u, u.y0, u.y1, u.y2);            // window of the 4 values before wt
-    u.l = lds32(lut + (g & 15u) * 4u);
-    u.h = lds32(lut + 64u + ((g >> 2) & 0x3cu));
-    u.c01 = __popc(g & 3u);                                // values at positions 0,1
-    u.c67 = __popc(g & 0xc0u);                             // values at positions 6,7
-    u.sb = w0 << 3;
-    u.st = wt << 3;
-#if SPB_PROBE == 1   // two more population counts (and the integer ops that keep them alive)
-    u.sb += (__popc(lo ^ 0x1234567u) << 5) + (__popc(hi | 0x10204080u) << 6);
-#elif SPB_PROBE == 2  // the same integer ops without the population counts
-    u.sb += ((lo ^ 0x1234567u) << 5) + ((hi | 0x10204080u) << 6);
-#elif SPB_PROBE == 3  // one more conflict-free shared-memory load
-    u.sb += lds32(lut + ((lo ^ 0x1234567u) & 0x3cu)) << 5;
-#elif SPB_PROBE == 4  // eight more integer ops
-    { uint32_t z = lo ^ 0x1234567u; z = (z << 3) ^ hi; z = (z >> 5) + lo; z = (z << 7) ^ hi; z = (z >> 9) + lo; u.sb += z << 5; }
-#endif
-}
-// The same from a tile table entry: w = bitmap of the tile's rows 0-3 or 4-7 (the half this thread's row is in),
-// half = shared address of the first value of that half.
+// Load half for one row segment, from a tile table entry: w = bitmap of the tile's rows 0-3 or 4-7 (the half this
+// thread's row is in), half = shared address of the first value of that half.
 //   below   thread constant: bitmap bits of the rows of the half above this thread's row
 //   rsel    permute selector moving this row's mask byte to byte 0 of a zero word
 //   lutlane shared address of this lane's copy of the selector table
 __device__ __forceinline__ void unit_load3(uint32_t w, uint32_t half, uint32_t below, uint32_t rsel, uint32_t lutlane,
                                            UnitLoads& u)
 {
+#if SPB_IMAD
+    // Address arithmetic as multiply-adds: the integer ALU (logic, shifts, byte permutes, adds) is the busiest
+    // pipe of the decode warps, the multiply-add pipe is almost idle.
+    const uint32_t w0 = imad(__popc(w & below), 2u, half);
+    const uint32_t g = prmt(w, 0u, rsel);                  // row mask, zero-extended
+    const uint32_t wt = imad(__popc(g), 2u, w0);           // address just past the row's last value
+    lds32x3(w0 & ~3u, u.x0, u.x1, u.x2);
+    lds32x3_before(wt & ~3u, u.y0, u.y1, u.y2);            // window of the 4 values before wt
+    lds64(imad(g, 128u, lutlane), u.l, u.h);
+    u.c01 = __popc(g & 3u);                                // values at positions 0,1
+    u.c67 = __popc(g & 0xc0u);                             // values at positions 6,7
+    u.sb = imad(w0, 8u, 0u);
+    u.st = imad(wt, 8u, 0u);
+#else
     const uint32_t w0 = half + 2u * __popc(w & below);
     const uint32_t g = prmt(w, 0u, rsel);                  // row mask, zero-extended
     const uint32_t wt = w0 + 2u * __popc(g);               // address just past the row's last value
@@ -586,6 +563,7 @@ __device__ __forceinline__ void unit_load3(uint32_t w, uint32_t half, uint32_t b
     u.c67 = __popc(g & 0xc0u);                             // values at positions 6,7
     u.sb = w0 << 3;
     u.st = wt << 3;
+#endif
 }
 __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
 {
@@ -593,8 +571,13 @@ __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
     const uint32_t t0 = __funnelshift_r(u.y0, u.y1, u.st), t1 = __funnelshift_r(u.y1, u.y2, u.st);
     const uint32_t win_lo = 0x3210u + 0x2222u * u.c01, win_hi = 0x7654u - 0x2222u * u.c67;
     o[0] = prmt(b0, 0u, u.l);
+#if SPB_IMAD
+    o[1] = prmt(prmt(b0, b1, win_lo), 0u, __umulhi(u.l, 65536u));
+    o[2] = prmt(prmt(t0, t1, win_hi), 0u, __umulhi(u.h, 65536u));
+#else
     o[1] = prmt(prmt(b0, b1, win_lo), 0u, u.l >> 16);
     o[2] = prmt(prmt(t0, t1, win_hi), 0u, u.h >> 16);
+#endif
     o[3] = prmt(t1, 0u, u.h);
 }
 
@@ -607,8 +590,6 @@ template <int NPAD, bool kExchange, bool kBalanced>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtensorMap tmap_b)
 {
-    // selector tables: low nibble entries [0,16), high nibble entries [16,32)
-    __shared__ __align__(128) uint32_t lut_tab[32];
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled activation tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -631,7 +612,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     // Back-to-back tcgen05.mma into one accumulator are serialised by the tensor core, and at these
     // tiny N every instruction is pure latency, so the four k-steps of a k-tile go to different
     // accumulators (summed in the epilogue).
-    constexpr int kNAcc = 4;
+    constexpr int kNAcc = NPAD <= 16 ? 4 : 2;
     constexpr int kAccBufs = NPAD <= 32 ? 2 : 1;
     constexpr uint32_t kAccCols = kAccBufs * kNAcc * NPAD;
     constexpr uint32_t kACols = kABlocks * 32;
@@ -654,18 +635,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-#if SPB_SEG3
     for (uint32_t i = threadIdx.x; i < 256u * 16u; i += kThreads) {
         const uint32_t g = i >> 4;
         *reinterpret_cast<uint2*>(smem + 1024 + kTileTabBytes * 4 * kDecodeGroups + 8 * i) =
             make_uint2(lut_low_entry(g & 15u), lut_high_entry(g >> 4));
     }
-#else
-    if (threadIdx.x >= 32 && threadIdx.x < 64) {
-        const uint32_t n = threadIdx.x - 32;
-        lut_tab[n] = n < 16 ? lut_low_entry(n) : lut_high_entry(n - 16);
-    }
-#endif
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
                      "r"(kTmemCols)
@@ -857,19 +831,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 // one elected lane issues this warp's copies with warp-uniform operands
                 if (elect_one()) {
                     if (prole == 0) {
-#if SPB_PROBE_SKIP
-                        if (SPB_PROBE_SKIP & 4) { n0 = 0; n1 = 0; }
-                        const uint32_t tx = ((SPB_PROBE_SKIP & 1) ? 0u : (uint32_t)nv * kBTile) + n0 + n1 +
-                                            ((SPB_PROBE_SKIP & 2) ? 0u : (chunk1 ? 2u : 1u) * (uint32_t)nv * (512u + 16u));
-#else
                         const uint32_t tx =
                             (uint32_t)nv * kBTile + n0 + n1 + (chunk1 ? 2u : 1u) * (uint32_t)nv * (512u + 16u);
-#endif
                         mbar_expect_tx(full, tx);
                         if (n0) bulk_g2s(sbase + off_v0, p.vals + a0, n0, full);
                         if (n1) bulk_g2s(sbase + off_v1, p.vals + a1, n1, full);
-                    } else if ((SPB_PROBE_SKIP & 2) && prole == 1) {
-                    } else if ((SPB_PROBE_SKIP & 1) && prole == 2) {
                     } else if (prole == 1) {
                         bulk_g2s(sbase + off_bm0, p.bitmap + g0 * 64, (uint32_t)nv * 512u, full);
                         bulk_g2s(sbase + off_mt0, p.mtile + g0 * 4, (uint32_t)nv * 16u, full);
@@ -937,7 +903,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                             const uint64_t bdesc = make_b_desc(sbase + (uint32_t)sub * kBTile);
                             const uint32_t a_tmem = tmem_a0 + blk * 32;
 #pragma unroll
-                            for (int s = 0; s < SPB_PROBE_MMAS; ++s)
+                            for (int s = 0; s < 4; ++s)
                                 tc_mma_ts(d_tmem + (s % kNAcc) * NPAD, a_tmem + 8 * s, bdesc + 2 * s, idesc,
                                           (kk0 > 0 || sub > 0 || s >= kNAcc) ? 1u : 0u);
                             tc_commit(bar_afree + 8 * blk);
@@ -1170,52 +1136,34 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         }
     } else {
         // ================================================================= decode
-        // Decode group g (4 warps, one per TMEM lane quadrant) belongs to set g / kKT and expands k-tile
-        // g % kKT of every stage of its set.  Every warp works alone, one thread per weight row: a row
-        // crosses 8 bitmap tiles per k-tile; the thread reads their bitmaps, keeps a running sum of the
-        // tile sizes inside its 16-row median tile (the other tile of each pair is counted by the lane
-        // 8 away), finds its row's values with popcounts and expands them.
+        // Decode group g is four warps, one per TMEM lane quadrant, one thread per weight row.  The k-tiles of the
+        // CTA's stage sequence are cut into units of kUnit k-tiles of one stage and dealt to the groups in turn.
+        // Per unit a warp first works out, one tile per lane, where the values of its 32 tiles of each k-tile start
+        // (population count of the bitmap, prefix sum over the 16 tiles of a median tile by shuffles) and leaves
+        // {bitmap half, start of the half's values} pairs in its tile table; then every thread expands, for each of
+        // the 8 tiles its row crosses, its row segment and writes it to tensor memory.  The barrier checks and the
+        // prefix sums are a chain of dependent instructions: it is paid once per unit.
         if constexpr (kResize) reg_alloc<kRegsDecode>();
         const int dw = warp - kDecodeWarp0;
         const int group = dw >> 2;
         const int quad = warp & 3;             // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;      // weight row inside the 128-row block
-        const uint32_t lut = smem_u32(lut_tab);
         const int chunk = row >> 6, rr = row & 63;   // 64-row global-tile row of the block, row inside it
         const int r_in_tile = rr & 7;
         const uint32_t my_v = chunk ? off_v1 : off_v0;
-        // k-tile 0 of a stage: this row's median offset, its global tile's start, and the bitmap of the first
-        // of the row's 8 tiles (they are 16 bytes apart): median tile rr >> 4, row half (rr >> 3) & 1 of
-        // the 2 x 2 tile order
         const uint32_t rel0 = off_rel + 4 * (uint32_t)(chunk * kKT);
-        const uint32_t bm0 = (chunk ? off_bm1 : off_bm0) + 8 * (uint32_t)(16 * (rr >> 4) + ((rr >> 3) & 1));
-        // Lane l also looks after one of the 32 tiles of the warp's two median tiles per k-tile (tile l & 15 of
-        // median tile 2 * (quad & 1) + (l >> 4)): it works out where the tile's values start and leaves that in
-        // the warp's table, from which the row threads read the starts of the tiles they cross.
+        // Lane l looks after tile l & 15 of median tile 2 * (quad & 1) + (l >> 4) of each k-tile of the unit.
         const uint32_t tile_tab = smem_u32(smem + 1024) + (uint32_t)dw * kTileTabBytes;
-#if SPB_SEG3
-        // this row's entry of the table for its first tile (the others are 32 bytes apart), the half its row is in
+        const uint32_t tile_bm0 = (chunk ? off_bm1 : off_bm0) + 8 * (uint32_t)(32 * (quad & 1) + lane);
+        const uint32_t tile_mt0 = (chunk ? off_mt1 : off_mt0) + 4 * (uint32_t)(2 * (quad & 1) + (lane >> 4));
+        // This row's entry of the table for the first tile it crosses (the others are 32 bytes apart: the tiles of a
+        // median tile are stored in pairs, rows 0-7 then rows 8-15 of each 8-column step), the half its row is in.
         const uint32_t ent = tile_tab + 16 * (uint32_t)(16 * (lane >> 4) + ((lane >> 3) & 1)) + 8 * (uint32_t)(r_in_tile >> 2);
         const uint32_t below = (r_in_tile & 3) ? (1u << (8 * (r_in_tile & 3))) - 1u : 0u;
         const uint32_t rsel4 = 0x4440u | (uint32_t)(r_in_tile & 3);
         const uint32_t lutlane = smem_u32(smem + 1024 + kTileTabBytes * 4 * kDecodeGroups) + 8 * (uint32_t)(lane & 15);
-#endif
-        const uint32_t tile_bm0 = (chunk ? off_bm1 : off_bm0) + 8 * (uint32_t)(32 * (quad & 1) + lane);
-        const uint32_t tile_mt0 = (chunk ? off_mt1 : off_mt0) + 4 * (uint32_t)(2 * (quad & 1) + (lane >> 4));
-        const uint32_t tile_sel = 4 * (uint32_t)(16 * (lane >> 4) + ((lane >> 3) & 1));  // offset inside a table
-        const uint32_t below_lo = r_in_tile < 4 ? (1u << (8 * r_in_tile)) - 1u : 0xffffffffu;
-        const uint32_t below_hi = r_in_tile <= 4 ? 0u : (1u << (8 * (r_in_tile - 4))) - 1u;
-        const uint32_t rsel = 0x4440u | (uint32_t)r_in_tile;
 
-        // The k-tiles of the stages are dealt to the groups in turn, across stages and work items: k-tile j of
-        // a stage goes to group (j + rot) % kKT, rot = k-tiles dealt so far.  A stage with fewer than kKT
-        // k-tiles (the end of a work item) then costs no more than the k-tiles it has.
         uint32_t slot = 0, round = 0, rot = 0, tb = 0, ph = 0, used = 0;
-        const uint32_t tsel = tile_tab + tile_sel;
-        // The start of a k-tile (barrier checks, tile starts) is a chain of dependent instructions, its body is
-        // bound by arithmetic throughput.  Because no group ever waits for another one (see the A block
-        // barriers), the groups drift apart after the first k-tiles, and one group's chains then overlap the
-        // others' arithmetic on every scheduler; starting them apart on purpose measured the same.
         bool ok = true;
         Walk wk;
         wk.template init<kBalanced>(p);
@@ -1227,101 +1175,92 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             const bool valid = chunk == 0 || (2 * w.y + 1) < p.gm_total;
             for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT) {
                 const int nv = min(kKT, w.nk - kk0);
-                const int sub = (int)(((uint32_t)group + (uint32_t)kDecodeGroups - rot) % (uint32_t)kDecodeGroups);  // this group's k-tile
-                rot = (rot + (uint32_t)nv) % (uint32_t)kDecodeGroups;
-                const uint32_t blk = (tb + (uint32_t)sub) % kABlocks;
-                // Every group, with or without a k-tile, waits for the stage: it arrives on the stage's empty
+                const int nun = (nv + kUnit - 1) / kUnit;  // units in this stage
+                const int usub = (int)(((uint32_t)group + (uint32_t)kDecodeGroups - rot) % (uint32_t)kDecodeGroups);  // this group's unit
+                rot = (rot + (uint32_t)nun) % (uint32_t)kDecodeGroups;
+                // Every group, with or without a unit, waits for the stage: it arrives on the stage's empty
                 // barrier below and must not get a ring round ahead of it.
                 PROF_T(0);
                 ok = mbar_wait(bar_full + 8 * slot, round & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 PROF_T(1);
-                if (sub < nv) {
+                if (usub < nun) {
+                    const int sub0 = usub * kUnit, nk = min(kUnit, nv - sub0);  // the unit's k-tiles of the stage
                     const uint32_t st = stage0 + slot * stage_bytes;
-                    {   // starts of the warp's 32 tiles: running sum of the tile sizes inside each median tile
-                        uint32_t lo = 0u, hi = 0u, base = st + my_v;
-                        if (valid) {
-                            lds64(st + tile_bm0 + (uint32_t)sub * 512, lo, hi);
-                            const uint32_t mt = lds32(st + tile_mt0 + (uint32_t)sub * 16);
-                            const uint32_t rel = lds32(st + rel0 + 4 * (uint32_t)sub);
-                            // clamped so that corrupt offsets can never point outside the stage
-                            base += min(rel + 2 * mt, (uint32_t)kKT * vmax);
+                    {   // starts of the warp's 32 tiles of each k-tile: running sum of the tile sizes inside each median tile
+                        uint32_t lo[kUnit], hi[kUnit], base[kUnit], cnt[kUnit], x[kUnit];
+#pragma unroll
+                        for (int j = 0; j < kUnit; ++j) {
+                            lo[j] = hi[j] = 0u;
+                            base[j] = st + my_v;
+                            if (valid && j < nk) {
+                                lds64(st + tile_bm0 + (uint32_t)(sub0 + j) * 512, lo[j], hi[j]);
+                                const uint32_t mt = lds32(st + tile_mt0 + (uint32_t)(sub0 + j) * 16);
+                                const uint32_t rel = lds32(st + rel0 + 4 * (uint32_t)(sub0 + j));
+                                // clamped so that corrupt offsets can never point outside the stage
+                                base[j] += min(rel + 2 * mt, (uint32_t)kKT * vmax);
+                            }
                         }
-                        const uint32_t cnt = __popc(lo) + __popc(hi);
-                        uint32_t x = cnt;
+#pragma unroll
+                        for (int j = 0; j < kUnit; ++j) x[j] = cnt[j] = __popc(lo[j]) + __popc(hi[j]);
 #pragma unroll
                         for (int d = 1; d < 16; d <<= 1) {
-                            const uint32_t y = __shfl_up_sync(0xffffffffu, x, d, 16);
-                            if ((lane & 15) >= d) x += y;
+#pragma unroll
+                            for (int j = 0; j < kUnit; ++j) {
+                                const uint32_t y = __shfl_up_sync(0xffffffffu, x[j], d, 16);
+                                if ((lane & 15) >= d) x[j] += y;
+                            }
                         }
-                        __syncwarp();  // every lane has read the previous k-tile's table
-#if SPB_SEG3
-                        {
-                            const uint32_t ts_lo = base + 2 * (x - cnt), ts_hi = ts_lo + 2 * __popc(lo);
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_tab + 16 * (uint32_t)lane), "r"(lo),
-                                         "r"(ts_lo), "r"(hi), "r"(ts_hi)
+                        __syncwarp();  // every lane has read the previous unit's tables
+#pragma unroll
+                        for (int j = 0; j < kUnit; ++j) {
+                            const uint32_t ts_lo = base[j] + 2 * (x[j] - cnt[j]), ts_hi = ts_lo + 2 * __popc(lo[j]);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_tab + 512 * j + 16 * (uint32_t)lane),
+                                         "r"(lo[j]), "r"(ts_lo), "r"(hi[j]), "r"(ts_hi)
                                          : "memory");
                         }
-#else
-                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile_tab + 4 * (uint32_t)lane), "r"(base + 2 * (x - cnt))
-                                     : "memory");
-#endif
                         __syncwarp();
                     }
                     PROF_T(2);
-                    // the MMAs of the block's previous k-tile (they ran while the tile starts were worked out)
-                    if ((used >> blk) & 1u) ok = mbar_wait(bar_afree + 8 * blk, ((ph >> blk) & 1u) ^ 1u, abort_flag);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    tc_fence_after();
-                    PROF_T(3);
-                    const uint32_t ta = tmem_a0 + blk * 32 + ((uint32_t)(quad * 32) << 16);
-                    const uint32_t sp_bm = st + bm0 + (uint32_t)sub * 512;
-                    uint32_t a[32];
 #pragma unroll
-#if SPB_SEG3
-                    for (int q0 = 0; q0 < SPB_PROBE_SEGS; q0 += 2) {
-                        uint32_t wq[2], hq[2];
-                        UnitLoads u[2];
+                    for (int j = 0; j < kUnit; ++j) {
+                        if (j >= nk || !ok) continue;
+                        const uint32_t blk = (tb + (uint32_t)(sub0 + j)) % kABlocks;
+                        // the MMAs of the block's previous k-tile
+                        if ((used >> blk) & 1u) ok = mbar_wait(bar_afree + 8 * blk, ((ph >> blk) & 1u) ^ 1u, abort_flag);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) continue;
+                        tc_fence_after();
+                        PROF_T(3);
+                        const uint32_t ta = tmem_a0 + blk * 32 + ((uint32_t)(quad * 32) << 16);
+                        uint32_t a[32];
 #pragma unroll
-                        for (int q = 0; q < 2; ++q) lds64(ent + 32 * (q0 + q), wq[q], hq[q]);
+                        for (int q0 = 0; q0 < 8; q0 += 2) {
+                            uint32_t wq[2], hq[2];
+                            UnitLoads u[2];
 #pragma unroll
-                        for (int q = 0; q < 2; ++q) unit_load3(wq[q], hq[q], below, rsel4, lutlane, u[q]);
+                            for (int q = 0; q < 2; ++q) lds64(ent + 512 * j + 32 * (q0 + q), wq[q], hq[q]);
 #pragma unroll
-                        for (int q = 0; q < 2; ++q) unit_expand(u[q], a + 4 * (q0 + q));
-                        tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
-                    }
-#else
-                    for (int q0 = 0; q0 < SPB_PROBE_SEGS; q0 += 2) {
-                        uint32_t blo[2], bhi[2];
-                        UnitLoads u[2];
+                            for (int q = 0; q < 2; ++q) unit_load3(wq[q], hq[q], below, rsel4, lutlane, u[q]);
 #pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            blo[q] = bhi[q] = 0u;
-                            if (valid) lds64(sp_bm + 16 * (q0 + q), blo[q], bhi[q]);
+                            for (int q = 0; q < 2; ++q) unit_expand(u[q], a + 4 * (q0 + q));
+                            tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
                         }
-#pragma unroll
-                        for (int q = 0; q < 2; ++q)
-                            unit_load(blo[q], bhi[q], lds32(tsel + 8 * (q0 + q)), below_lo, below_hi, rsel, lut, u[q]);
-#pragma unroll
-                        for (int q = 0; q < 2; ++q) unit_expand(u[q], a + 4 * (q0 + q));
-                        tc_st_32x32b_x8(ta + 4 * q0, a + 4 * q0);
-                    }
-#endif
-                    PROF_T(4);
-                    tc_wait_st();
-                    tc_fence_before();
-                    PROF_T(5);
+                        PROF_T(4);
+                        tc_wait_st();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_aready + 8 * blk);
+                        PROF_T(5);
 #if SPB_PROF
-                    ++pacc[7];
+                        ++pacc[7];
 #endif
+                    }
+                    if (!ok) break;
                 }
                 __syncwarp();
-                if (lane == 0) {
-                    if (sub < nv) mbar_arrive(bar_aready + 8 * blk);
-                    mbar_arrive(bar_empty + 8 * slot);
-                }
+                if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
                 const uint32_t mask = block_mask(tb, nv);
                 used |= mask;
                 ph ^= mask;

@@ -87,3 +87,40 @@ def test_split_k_suggestion_and_schedule_switch_without_gpu(lib_built):
     lib.spb_set_schedule(0)
     assert lib.spb_suggest_split_k(28672, 16, 7168) == 1    # balanced shares fill the SMs without one
     assert lib.spb_set_schedule(7) == -1 and lib.spb_set_schedule(0) == 0
+
+
+def test_spmm_entry_points_reject_bad_arguments_without_launching(lib_built):
+    """Shapes, null pointers and misaligned pointers are turned into error codes before any CUDA call is made, by the
+    plain entry point and by the fused all-gather one alike (bulk copies and tensor maps fault on the device on a
+    pointer that is not 16-byte aligned)."""
+    from spmspm_b200 import _lib
+    lib = _lib.load()
+    INVALID, MISALIGNED = 1, 716          # cudaErrorInvalidValue, cudaErrorMisalignedAddress
+    ok = 0x10000                          # never dereferenced: every call below fails its checks first
+    args = dict(vals=ok, gt=ok, mt=ok, bm=ok, mx=ok, B=ok, C=ok, ws=ok)
+
+    def spmm(M=128, N=16, K=128, sk=1, **over):
+        a = dict(args, **over)
+        return lib.spb_spmm_bitmap_v3(None, None, a["vals"], a["gt"], a["mt"], a["bm"], a["mx"], a["B"], a["C"], M, N, K,
+                                      a["ws"], sk)
+
+    assert spmm(M=100) == INVALID and spmm(K=0) == INVALID and spmm(N=0) == INVALID
+    assert spmm(sk=3) == INVALID                      # more ranges than k-tiles
+    assert spmm(vals=None) == INVALID and spmm(C=None) == INVALID and spmm(sk=2, ws=None) == INVALID
+    for name in ("vals", "mt", "bm", "B", "C"):
+        assert spmm(**{name: ok + 2}) == MISALIGNED, name
+    assert spmm(sk=2, ws=ok + 8) == MISALIGNED
+    assert b"16-byte" in lib.spb_last_error()
+
+    peers = (ctypes.c_void_p * 2)(ok, ok)
+
+    def gather(M=128, N=16, K=128, sk=1, n_peers=2, rank=0, M_full=256, row0=0, **over):
+        a = dict(args, **over)
+        return lib.spb_spmm_bitmap_v3_allgather(None, a["vals"], a["gt"], a["mt"], a["bm"], a["mx"], a["B"], peers, peers,
+                                                n_peers, rank, M, N, K, M_full, row0, None, a["ws"], sk)
+
+    assert gather(n_peers=9) == INVALID and gather(rank=2) == INVALID and gather(row0=192) == INVALID
+    assert gather(M=96) == INVALID and gather(vals=None) == INVALID and gather(sk=2, ws=None) == INVALID
+    for name in ("vals", "mt", "bm", "B"):
+        assert gather(**{name: ok + 4}) == MISALIGNED, name
+    assert gather(sk=2, ws=ok + 2) == MISALIGNED
