@@ -111,8 +111,10 @@ int spb_load_bin_files(const char* val, const char* gtile, const char* mtile, co
  * the k-tiles are cut into Split_K ranges exactly as the reference does
  * (csrc/SpMM_Kernel.cuh:35-43), fp16 partials go to Reduction_Workspace
  * ([Split_K][N][M], at least Split_K*M*N halves) and are summed in fp32 in range
- * order (csrc/Reduction_Kernel.cuh:24-44).  Asynchronous on `stream`; allocates
- * nothing on the device.
+ * order (csrc/Reduction_Kernel.cuh:24-44).  Asynchronous on `stream`; never
+ * allocates, frees or synchronises (like the reference's entry point); the first
+ * call on a device raises the kernels' shared-memory limit (cudaFuncSetAttribute),
+ * which spb_init also does.
  * N may be any positive value (the reference accepts only 8,16,32,64 and
  * multiples of 128; csrc/SpMM_API.cuh:60-96).  Returns a cudaError_t value;
  * invalid shapes give cudaErrorInvalidValue and launch nothing.
@@ -134,7 +136,8 @@ int spb_spmm_bitmap_v3(void* stream, const uint16_t* A, const uint16_t* Compress
  *   - Split_K*M*N*2 bytes must fit the array; larger requests fail with cudaErrorInvalidValue and
  *     launch nothing.  Split_K == 1 needs no scratch and has no size limit.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
- *     prepares the kernel; make that first call outside any stream capture.
+ *     raises the shared-memory limit of the kernels of every activation width at once; make that
+ *     first call (or a call of spb_init) outside any stream capture.
  *   - All calls share the one array and it keeps whatever the previous call left; the kernels
  *     overwrite every partial they later read, so no clearing is needed, but two calls whose
  *     kernels overlap on the GPU (different streams) race on it: serialise them.
@@ -144,6 +147,16 @@ int spb_spmm_bitmap_v3(void* stream, const uint16_t* A, const uint16_t* Compress
 int spb_spmm_bitmap_v3_noalloc(void* stream, const uint16_t* Compressed_A, const int* TileOffsets,
                                const int* TileOffsets_Median, const uint64_t* bitmap, const int* max_nnz_intile,
                                const uint16_t* B, uint16_t* C, int M_Global, int N_Global, int K_Global, int Split_K);
+
+/*
+ * One-time preparation of (current device, stream), no counterpart in the reference: raises the kernels'
+ * shared-memory limit and creates the library-owned scratch (about 14 MB of partial sums and arrival counters)
+ * that the balanced work schedule and the fused all-gather use on that stream.  Allocates device memory and
+ * synchronises the device, so call it once per stream at start-up, outside stream capture (up to 8 streams per
+ * device).  Without it every SpMM entry point still works, under the static schedule, and still allocates
+ * nothing; spb_spmm_bitmap_v3_allgather needs it.
+ */
+int spb_init(void* stream);
 
 /*
  * Split-K reduction alone.  Replaces the SplitK_Reduction launch
@@ -165,11 +178,10 @@ int spb_suggest_split_k(int M, int N, int K);
  *   SPB_SCHEDULE_STATIC: one work item per 128-row block and split-K range, no scratch.
  *   SPB_SCHEDULE_BALANCED: the k-tiles of all ranges are laid end to end and every SM takes an equal
  *     share; a range that is cut between SMs is summed in fp32 through scratch memory the library owns
- *     (about 14 MB per stream, created on a stream's first call), and rounded to fp16 once, where the
- *     reference rounds it.  The scratch belongs to the stream: a call captured into a CUDA graph uses
- *     the scratch an earlier, uncaptured call on the capturing stream created (the static schedule if
- *     there was none), so such a graph must not run at the same time as other calls made on that
- *     stream.  Calls on more than 8 streams and spb_spmm_bitmap_v3_noalloc use the static schedule.
+ *     (about 14 MB per stream, created by spb_init), and rounded to fp16 once, where the reference
+ *     rounds it.  The scratch belongs to the stream: a graph captured on a stream must not run at the
+ *     same time as other calls made on that stream.  Calls on a stream spb_init was not called for, and
+ *     spb_spmm_bitmap_v3_noalloc, use the static schedule.
  *   SPB_SCHEDULE_AUTO (default): per call, whichever of the two a cost model expects to be faster.
  * Both give the same result up to the order of the fp32 additions inside a range.
  * Returns the previous mode, or -1 for an invalid mode.  Process-wide.
@@ -196,8 +208,7 @@ int spb_set_schedule(int mode);
  * in; it counts as the one consumer of that exchange (do not also call spb_wait_flags for it).
  * With Split_K > 1 the fp16 partial sums go to Reduction_Workspace (Split_K*M_shard*N_Global halves) as in
  * spb_spmm_bitmap_v3 and the reduction kernel does the stores to the peers and the flags.
- * Peer memory is only ever written, never loaded from.  Needs the scratch of the calling stream (see
- * spb_set_schedule): the first call on a stream must not be captured.
+ * Peer memory is only ever written, never loaded from.  Needs spb_init on the calling stream.
  */
 int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compressed_A, const int* TileOffsets,
                                  const int* TileOffsets_Median, const uint64_t* bitmap, const int* max_nnz_intile,

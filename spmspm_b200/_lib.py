@@ -36,6 +36,7 @@ SIGNATURES = {
     "spb_splitk_reduce": (ctypes.c_int, [_vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "spb_suggest_split_k": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "spb_set_schedule": (ctypes.c_int, [ctypes.c_int]),
+    "spb_init": (ctypes.c_int, [_vp]),
     "spb_spmm_bitmap_v3_allgather": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,
                                                     ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _vp, ctypes.c_int]),
     "spb_wait_flags": (ctypes.c_int, [_vp, _vp, ctypes.c_int]),

@@ -271,6 +271,27 @@ def spmm_splitk_api_bitmap_v3(stream, A, Compressed_A, TileOffsets, TileOffsets_
     _check(code, "SpMM_SplitK_API_bitmap_v3")
 
 
+_initialised = set()
+
+
+def init(stream=None):
+    """spb_init for the current device and `stream` (default: torch's current stream): creates the scratch of the
+    balanced schedule and of the fused all-gather.  Allocates and synchronises; not during stream capture."""
+    s = stream if stream is not None else torch.cuda.current_stream()
+    key = (torch.cuda.current_device(), s.cuda_stream)
+    if key not in _initialised:
+        _check(_lib.load().spb_init(ctypes.c_void_p(s.cuda_stream)), "spb_init")
+        _initialised.add(key)
+
+
+def _init_if_possible(stream):
+    """The Python wrappers prepare a stream the first time they see it, unless it is being captured (the C entry
+    points never do: they fall back to the static schedule on a stream spb_init was not called for)."""
+    s = stream if stream is not None else torch.cuda.current_stream()
+    if (torch.cuda.current_device(), s.cuda_stream) not in _initialised and not torch.cuda.is_current_stream_capturing():
+        init(s)
+
+
 def suggest_split_k(M, N, K):
     return _lib.load().spb_suggest_split_k(M, N, K)
 
@@ -298,6 +319,7 @@ def spmm(W: BitmapMatrix, B, split_k=None, out=None, workspace=None, stream=None
     if split_k > 1 and workspace is None:
         workspace = torch.empty(split_k * N * W.M, dtype=torch.float16, device=B.device)
     with torch.cuda.device(B.device):
+        _init_if_possible(stream)
         spmm_splitk_api_bitmap_v3(stream, None, W.vals, W.gtile, W.mtile, W.bitmap, W.max_nnz, B, out, W.M, N, W.K,
                                   workspace, split_k)
     return out
@@ -309,7 +331,11 @@ def spmm_noalloc(W: BitmapMatrix, B, split_k, out, stream=None):
     For callers that must not allocate device memory: `out` has to be supplied, nothing is allocated here or in
     the library.  Raises SpmmError when split_k * M * N * 2 bytes exceed the built-in array.
     """
+    if not (B.is_cuda and B.dtype == torch.float16 and B.dim() == 2 and B.is_contiguous() and B.shape[1] == W.K):
+        raise SpmmError("B must be a contiguous CUDA float16 [N,K] tensor")
     N = B.shape[0]
+    if not (out.is_cuda and out.dtype == torch.float16 and out.is_contiguous() and tuple(out.shape) == (N, W.M)):
+        raise SpmmError("out must be a contiguous CUDA float16 [N,M] tensor")
     with torch.cuda.device(B.device):
         code = _lib.load().spb_spmm_bitmap_v3_noalloc(_stream_ptr(stream), _ptr(W.vals), _ptr(W.gtile), _ptr(W.mtile),
                                                       _ptr(W.bitmap), _ptr(W.max_nnz), _ptr(B), _ptr(out), W.M, N, W.K,
@@ -329,6 +355,7 @@ def spmm_allgather(W: BitmapMatrix, B, C_peers, flag_peers, n_peers, rank, M_ful
     if split_k > 1 and workspace is None:
         workspace = torch.empty(split_k * B.shape[0] * W.M, dtype=torch.float16, device=B.device)
     with torch.cuda.device(B.device):
+        _init_if_possible(stream)
         code = _lib.load().spb_spmm_bitmap_v3_allgather(_stream_ptr(stream), _ptr(W.vals), _ptr(W.gtile), _ptr(W.mtile),
                                                         _ptr(W.bitmap), _ptr(W.max_nnz), _ptr(B), C_peers, flag_peers,
                                                         n_peers, rank, W.M, B.shape[0], W.K, M_full, row_offset,

@@ -414,6 +414,8 @@ int spb_splitk_reduce(void* stream, uint16_t* C, const uint16_t* Reduction_Works
 
 int spb_suggest_split_k(int M, int N, int K) { return spb::suggest_split_k(M, N, K); }
 
+int spb_init(void* stream) { return (int)spb::init_stream((cudaStream_t)stream); }
+
 int spb_set_schedule(int mode)
 {
     const int prev = spb::set_schedule(mode);

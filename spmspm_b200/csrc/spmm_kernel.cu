@@ -40,9 +40,6 @@
 #ifndef SPB_PROF
 #define SPB_PROF 0  // development only: per-phase clock sums of one decode warp, the MMA warp and a producer warp
 #endif
-#ifndef SPB_IMAD
-#define SPB_IMAD 1
-#endif
 #ifndef SPB_UNIT
 #define SPB_UNIT 1  // k-tiles a decode group expands per turn (2 measured 3 % slower: the decode warps are bound by
                     // instruction issue, so paying the chain of waits once per two k-tiles buys nothing)
@@ -450,13 +447,6 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
-// a * b + c on the multiply-add pipe (the compiler turns a * 2 + c written in C++ into integer-ALU shifts and adds)
-__device__ __forceinline__ uint32_t imad(uint32_t a, uint32_t b, uint32_t c)
-{
-    uint32_t d;
-    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
 __device__ __forceinline__ void tc_st_32x32b_x8(uint32_t taddr, const uint32_t* r)
 {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
@@ -539,20 +529,6 @@ __device__ __forceinline__ void lds32x3_before(uint32_t addr, uint32_t& a, uint3
 __device__ __forceinline__ void unit_load3(uint32_t w, uint32_t half, uint32_t below, uint32_t rsel, uint32_t lutlane,
                                            UnitLoads& u)
 {
-#if SPB_IMAD
-    // Address arithmetic as multiply-adds: the integer ALU (logic, shifts, byte permutes, adds) is the busiest
-    // pipe of the decode warps, the multiply-add pipe is almost idle.
-    const uint32_t w0 = imad(__popc(w & below), 2u, half);
-    const uint32_t g = prmt(w, 0u, rsel);                  // row mask, zero-extended
-    const uint32_t wt = imad(__popc(g), 2u, w0);           // address just past the row's last value
-    lds32x3(w0 & ~3u, u.x0, u.x1, u.x2);
-    lds32x3_before(wt & ~3u, u.y0, u.y1, u.y2);            // window of the 4 values before wt
-    lds64(imad(g, 128u, lutlane), u.l, u.h);
-    u.c01 = __popc(g & 3u);                                // values at positions 0,1
-    u.c67 = __popc(g & 0xc0u);                             // values at positions 6,7
-    u.sb = imad(w0, 8u, 0u);
-    u.st = imad(wt, 8u, 0u);
-#else
     const uint32_t w0 = half + 2u * __popc(w & below);
     const uint32_t g = prmt(w, 0u, rsel);                  // row mask, zero-extended
     const uint32_t wt = w0 + 2u * __popc(g);               // address just past the row's last value
@@ -563,7 +539,6 @@ __device__ __forceinline__ void unit_load3(uint32_t w, uint32_t half, uint32_t b
     u.c67 = __popc(g & 0xc0u);                             // values at positions 6,7
     u.sb = w0 << 3;
     u.st = wt << 3;
-#endif
 }
 __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
 {
@@ -571,13 +546,8 @@ __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
     const uint32_t t0 = __funnelshift_r(u.y0, u.y1, u.st), t1 = __funnelshift_r(u.y1, u.y2, u.st);
     const uint32_t win_lo = 0x3210u + 0x2222u * u.c01, win_hi = 0x7654u - 0x2222u * u.c67;
     o[0] = prmt(b0, 0u, u.l);
-#if SPB_IMAD
-    o[1] = prmt(prmt(b0, b1, win_lo), 0u, __umulhi(u.l, 65536u));
-    o[2] = prmt(prmt(t0, t1, win_hi), 0u, __umulhi(u.h, 65536u));
-#else
     o[1] = prmt(prmt(b0, b1, win_lo), 0u, u.l >> 16);
     o[2] = prmt(prmt(t0, t1, win_hi), 0u, u.h >> 16);
-#endif
     o[3] = prmt(t1, 0u, u.h);
 }
 
@@ -811,7 +781,11 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 if (!ok) break;
                 PROF_T(1);
                 uint32_t n0 = (uint32_t)(e0 - a0) * 2, n1 = chunk1 ? (uint32_t)(e1 - a1) * 2 : 0u;
-                if (e0 < a0 || n0 > (uint32_t)nv * vmax || (chunk1 && (e1 < a1 || n1 > (uint32_t)nv * vmax))) {
+                // Offsets of a well-formed matrix are non-negative multiples of 8 values (every global tile is
+                // padded to 16 bytes); anything else would make a bulk copy read from a wrong or misaligned address.
+                const bool bad0 = a0 < 0 || e0 < a0 || ((a0 | e0) & 7) || n0 > (uint32_t)nv * vmax;
+                const bool bad1 = chunk1 && (a1 < 0 || e1 < a1 || ((a1 | e1) & 7) || n1 > (uint32_t)nv * vmax);
+                if (bad0 || bad1) {
                     if (lane == 0 && prole == 0) atomicOr(p.status, (int)kStatusBadOffsets);
                     n0 = 0;
                     n1 = 0;
@@ -1340,9 +1314,10 @@ DeviceInfo device_info()
 
 // ---------------------------------------------------------------- scratch of the balanced schedule
 // Owned by the library, one set per (device, stream) so that calls on different streams never share
-// counters; calls on one stream are ordered by the stream.  Created on the first eligible call of a
-// stream (cudaMalloc, so never while the stream is being captured; a captured call uses the set an
-// earlier call on the capturing stream created, else the static schedule).
+// counters; calls on one stream are ordered by the stream.  Created by spb_init(stream) only: the SpMM
+// entry points themselves never allocate or synchronise (the reference's entry point is asynchronous and
+// allocation-free, reference csrc/SpMM_API.cuh:47-110); on a stream that was never initialised they use
+// the static schedule, which needs no scratch.
 constexpr int kScratchSets = 8;
 constexpr int kCounterCap = 1 << 20;
 struct ScratchSet {
@@ -1431,6 +1406,31 @@ bool prefer_balanced(int row_blocks, int n_tiles, int kt, int sk, int sms, int n
 }
 
 template <int NPAD>
+cudaError_t prepare_width(int dyn_smem)
+{
+    cudaError_t e = cudaFuncSetAttribute(spmm_bitmap_tcgen05_kernel<NPAD, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(spmm_bitmap_tcgen05_kernel<NPAD, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(spmm_bitmap_tcgen05_kernel<NPAD, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(spmm_bitmap_tcgen05_kernel<NPAD, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
+    return e;
+}
+// Raises the dynamic shared-memory limit of all kernel variants on the current device, the first time it is
+// called for that device.
+cudaError_t prepare_kernels(int dev, int dyn_smem)
+{
+    static std::mutex mu;
+    static bool done[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (done[dev]) return cudaSuccess;
+    cudaError_t e = prepare_width<16>(dyn_smem);
+    if (e == cudaSuccess) e = prepare_width<32>(dyn_smem);
+    if (e == cudaSuccess) e = prepare_width<64>(dyn_smem);
+    if (e == cudaSuccess) done[dev] = true;
+    return e;
+}
+
+template <int NPAD>
 cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, int* status)
 {
     EncodeTiledFn enc = get_encode_fn();
@@ -1497,9 +1497,8 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     const int mode = g_schedule.load();
     if (mode != 1 && t_static_depth == 0 && (units + 1) * di.sms < (1LL << 31) && p.num_items <= kCounterCap &&
         no_empty_range && (mode == 2 || prefer_balanced(p.row_blocks, p.n_tiles, p.kt_total, a.split_k, di.sms, NPAD))) {
-        // While the stream is being captured nothing may be allocated: the scratch of an earlier call
-        // on this stream is used if there is one.
-        if (const ScratchSet* sc = scratch_for(s, dev, di.sms, !stream_is_capturing(s))) {
+        // the scratch spb_init created for this stream, if it was called
+        if (const ScratchSet* sc = scratch_for(s, dev, di.sms, false)) {
             p.partials = sc->partials;
             p.counters = sc->counters;
             p.balanced = 1;
@@ -1508,10 +1507,9 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     }
     if (p.n_flags > 0 || p.wait_flags) {
         // the count of finished CTAs lives behind the arrival counters of the stream's scratch
-        const ScratchSet* sc = scratch_for(s, dev, di.sms, !stream_is_capturing(s));
+        const ScratchSet* sc = scratch_for(s, dev, di.sms, false);
         if (!sc) {
-            set_error("fused all-gather: no scratch for this stream (more than %d streams in use, or the first call "
-                      "on the stream is being captured)", kScratchSets);
+            set_error("fused all-gather: spb_init has not been called for this stream");
             return cudaErrorNotReady;
         }
         p.done = sc->counters + kCounterCap;
@@ -1523,11 +1521,9 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
                   : variant == 2 ? spmm_bitmap_tcgen05_kernel<NPAD, true, false>
                   : variant == 1 ? spmm_bitmap_tcgen05_kernel<NPAD, false, true>
                                  : spmm_bitmap_tcgen05_kernel<NPAD, false, false>;
-    static bool attr_set[64][4] = {};
-    if (!attr_set[dev][variant]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn_smem);
+    {   // every variant of every activation-tile width, once per device: a later call never changes a kernel attribute
+        cudaError_t e = prepare_kernels(dev, dyn_smem);
         if (e != cudaSuccess) return e;
-        attr_set[dev][variant] = true;
     }
     const long long work = p.balanced ? units : (long long)p.num_items;
     const int grid = work < di.sms ? (int)work : di.sms;
@@ -1553,10 +1549,9 @@ cudaError_t exchange_counter(cudaStream_t s, int** out)
     DeviceInfo di = device_info();
     int dev = 0;
     if (!di.ok || cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
-    const ScratchSet* sc = scratch_for(s, dev, di.sms, !stream_is_capturing(s));
+    const ScratchSet* sc = scratch_for(s, dev, di.sms, false);
     if (!sc) {
-        set_error("fused all-gather: no scratch for this stream (more than %d streams in use, or the first call on "
-                  "the stream is being captured)", kScratchSets);
+        set_error("fused all-gather: spb_init has not been called for this stream");
         return cudaErrorNotReady;
     }
     *out = sc->counters + kCounterCap + 1;
@@ -1576,6 +1571,32 @@ extern "C" int spb_debug_prof(unsigned long long* out, int clear)
 }
 namespace spb {
 #endif
+// Creates the scratch of the balanced schedule and of the fused exchange for (current device, stream) and raises
+// the kernels' shared-memory limit; allocates and synchronises, so it must run outside stream capture.
+cudaError_t init_stream(cudaStream_t s)
+{
+    DeviceInfo di = device_info();
+    int dev = 0;
+    if (!di.ok || cudaGetDevice(&dev) != cudaSuccess) {
+        set_error("spb_init: no usable CUDA device");
+        return cudaErrorNoDevice;
+    }
+    if (stream_is_capturing(s)) {
+        set_error("spb_init: the stream is being captured");
+        return cudaErrorStreamCaptureUnsupported;
+    }
+    cudaError_t e = prepare_kernels(dev, di.max_smem - 1024);
+    if (e != cudaSuccess) return e;
+    int* status = nullptr;
+    e = device_status_ptr(&status);
+    if (e != cudaSuccess) return e;
+    if (!scratch_for(s, dev, di.sms, true)) {
+        set_error("spb_init: no scratch set left (%d streams per device) or out of device memory", kScratchSets);
+        return cudaErrorMemoryAllocation;
+    }
+    return cudaSuccess;
+}
+
 int set_schedule(int mode)
 {
     if (mode < 0 || mode > 2) return -1;

@@ -58,6 +58,8 @@ def _run(sp, A, B, split_k):
     (4096, 4096, 16, 0.5, 6),
     (5120, 5120, 16, 0.6, 6),    # OPT-13B out-proj
     (5120, 20480, 8, 0.6, 8),    # OPT-13B FC2
+    (128, 640, 16, 0.5, 7),      # 10 k-tiles in 7 ranges of 2: the last two ranges are empty and must come out as zeros
+    (128, 512, 16, 0.5, 7),      # 8 k-tiles in 7 ranges of 2: three empty ranges
 ])
 def test_spmm_matches_fp32_oracle(sp, M, K, N, s, sk):
     A = make_sparse(M, K, s, seed=M + 3 * K + N)
@@ -251,3 +253,41 @@ def test_stream_and_repeat_calls(sp):
     s.synchronize()
     for C in outs:
         _assert_close(C.cpu().numpy(), ref)
+
+
+def test_entry_point_allocates_nothing_until_spb_init(sp):
+    """spb_spmm_bitmap_v3 on a stream spb_init was never called for: no device memory is taken (the balanced
+    schedule's scratch is created by spb_init only) and the result is right; after spb_init the scratch exists."""
+    import ctypes
+    from spmspm_b200 import _lib
+    lib = _lib.load()
+    A = make_sparse(5120, 1024, 0.6, seed=91)
+    B = torch.from_numpy(make_dense(16, 1024, seed=92)).cuda()
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    ref = oracle.gemm_f32(A, B.cpu().numpy())
+    out = torch.zeros((16, 5120), dtype=torch.float16, device="cuda")
+    st = torch.cuda.Stream()
+    sp.set_schedule(sp.SCHEDULE_BALANCED)
+    try:
+        def call():
+            code = lib.spb_spmm_bitmap_v3(ctypes.c_void_p(st.cuda_stream), None, ctypes.c_void_p(W.vals.data_ptr()),
+                                          ctypes.c_void_p(W.gtile.data_ptr()), ctypes.c_void_p(W.mtile.data_ptr()),
+                                          ctypes.c_void_p(W.bitmap.data_ptr()), ctypes.c_void_p(W.max_nnz.data_ptr()),
+                                          ctypes.c_void_p(B.data_ptr()), ctypes.c_void_p(out.data_ptr()), 5120, 16, 1024,
+                                          None, 1)
+            assert code == 0, _lib.last_error()
+            st.synchronize()
+        torch.cuda.synchronize()
+        call()                                   # first call on the device may load the module
+        free0 = torch.cuda.mem_get_info()[0]
+        call()
+        assert torch.cuda.mem_get_info()[0] == free0
+        _assert_close(out.cpu().numpy(), ref)
+        sp.init(st)
+        assert torch.cuda.mem_get_info()[0] < free0
+        out.zero_()
+        call()                                   # now under the balanced schedule
+        _assert_close(out.cpu().numpy(), ref)
+    finally:
+        sp.set_schedule(sp.SCHEDULE_AUTO)
+    assert sp.device_status() == 0

@@ -14,6 +14,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 torch = pytest.importorskip("torch")
+import oracle  # noqa: E402
 from conftest import make_dense, make_sparse  # noqa: E402
 
 REL = 1e-2  # the tolerance of tests/test_gpu_spmm.py
@@ -31,7 +32,9 @@ def test_noalloc_entry_point_matches_regular_entry_point(lib_built):
     from spmspm_b200 import _lib
 
     lib = _lib.load()
-    cases = [(1024, 2048, 16, 0.6, 4, 11), (512, 1024, 32, 0.5, 3, 12)]  # M, K, N, sparsity, split_k, seed
+    # M, K, N, sparsity, split_k, seed; the last two leave split-K ranges empty (10 and 8 k-tiles in 7 ranges of 2):
+    # their partials must come out as zeros although the shared scratch still holds the previous call's sums
+    cases = [(1024, 2048, 16, 0.6, 4, 11), (512, 1024, 32, 0.5, 3, 12), (128, 640, 16, 0.5, 7, 13), (128, 512, 16, 0.5, 7, 14)]
     for M, K, N, s, sk, seed in cases:  # two calls in a row on the shared scratch
         A = make_sparse(M, K, s, seed)
         B = torch.from_numpy(make_dense(N, K, seed + 100)).cuda()
@@ -52,6 +55,7 @@ def test_noalloc_entry_point_matches_regular_entry_point(lib_built):
         torch.cuda.synchronize()
         assert _close(got.cpu().numpy(), want.cpu().numpy())
         assert _close(got.cpu().numpy(), balanced.cpu().numpy())
+        assert _close(got.cpu().numpy(), oracle.gemm_f32(A, B.cpu().numpy()))   # and against the fp32 host GEMM
         # same kernels, same split, same schedule: the two paths are in fact bit-identical
         assert np.array_equal(got.cpu().numpy().view(np.uint16), want.cpu().numpy().view(np.uint16))
     assert sp.device_status() == 0
