@@ -159,6 +159,20 @@ int spb_spmm_bitmap_v3_noalloc(void* stream, const uint16_t* Compressed_A, const
 int spb_init(void* stream);
 
 /*
+ * Launch overlap of consecutive SpMM calls on one stream (no counterpart in the reference).  The SpMM kernel is
+ * launched with programmatic stream serialization; with the setting on (default) its weight-streaming warps start
+ * fetching Compressed_A, the offsets, the bitmaps and max_nnz_intile as soon as its thread blocks are resident,
+ * while the slowest thread blocks of the stream's preceding kernel are still running; activations, outputs,
+ * workspaces and all scratch are only touched after that kernel has completed.  This is safe whenever the weight
+ * arrays are not written by a kernel that can still be running when the SpMM's thread blocks start, which holds
+ * for everything that does not itself release its dependents early (this library's SpMM kernels do, and never
+ * write weights).  Turn it off (0) if a kernel that releases its dependents early (griddepcontrol.launch_dependents /
+ * cudaTriggerProgrammaticLaunchCompletion) writes weight arrays right before an SpMM on the same stream.
+ * Returns the previous setting.  Process-wide.
+ */
+int spb_set_weight_prefetch(int on);
+
+/*
  * Split-K reduction alone.  Replaces the SplitK_Reduction launch
  * (csrc/SpMM_API.cuh:106-108, csrc/Reduction_Kernel.cuh:24-44).
  */

@@ -106,8 +106,11 @@ static cudaError_t spmm_checked(cudaStream_t stream, const uint16_t* vals, const
     a.N = N;
     a.K = K;
     a.split_k = split_k;
+    bool fused = false;
+    a.final_out = C;
+    a.reduce_fused = &fused;
     cudaError_t e = spmm_launch(stream, a);
-    if (e != cudaSuccess || split_k == 1) return e;
+    if (e != cudaSuccess || split_k == 1 || fused) return e;
     return splitk_reduce(stream, C, ws, M, N, split_k);
 }
 
@@ -415,6 +418,8 @@ int spb_splitk_reduce(void* stream, uint16_t* C, const uint16_t* Reduction_Works
 int spb_suggest_split_k(int M, int N, int K) { return spb::suggest_split_k(M, N, K); }
 
 int spb_init(void* stream) { return (int)spb::init_stream((cudaStream_t)stream); }
+
+int spb_set_weight_prefetch(int on) { return spb::set_weight_prefetch(on); }
 
 int spb_set_schedule(int mode)
 {

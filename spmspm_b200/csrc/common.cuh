@@ -38,10 +38,15 @@ struct SpmmArgs {
     const int* max_nnz;
     const uint16_t* B;
     uint16_t* out;  // C when split_k == 1, else the fp16 partial workspace
+    // split_k > 1: where the reduced result belongs (C), so that the kernel may do the reduction itself; when it
+    // does, *reduce_fused is set and the caller must not launch the reduction
+    uint16_t* final_out = nullptr;
+    bool* reduce_fused = nullptr;
     int M, N, K, split_k;
-    // Fused all-gather (n_out > 0, split_k == 1): the result rows go to rows row0.. of n_out buffers
-    // [N][ld_out] (this GPU's and its peers'), then entry flag_index of n_flags flag arrays gets the
-    // launch's sequence number (the incremented value of *sequence).
+    // Fused all-gather (n_out > 0): the result rows go to rows row0.. of n_out buffers [N][ld_out] (this GPU's
+    // and its peers'), then entry flag_index of n_flags flag arrays gets the launch's sequence number (the
+    // incremented value of *sequence).  With split_k > 1 that happens only if the kernel fuses the reduction
+    // (*reduce_fused); otherwise the caller's reduction launch has to store the rows and write the flags.
     uint16_t* outs[8] = {};
     uint32_t* flags[8] = {};
     int n_out = 0, ld_out = 0, row0 = 0, n_flags = 0, flag_index = 0;
@@ -58,7 +63,8 @@ int suggest_split_k(int M, int N, int K);
 // Work schedule of the SpMM kernel: 1 = static (one work item per split-K range, no scratch), 2 = balanced
 // (equal k-tile shares per SM, fp32 exchange through library-owned scratch) whenever possible, 0 = whichever
 // the cost model expects to be faster for the shape.
-int set_schedule(int mode);          // returns the previous mode, -1 for an invalid one
+int set_schedule(int mode);
+int set_weight_prefetch(int on);     // returns the previous setting          // returns the previous mode, -1 for an invalid one
 void push_static_schedule();         // calling thread only, nestable
 void pop_static_schedule();
 cudaError_t reset_schedule_scratch();  // clears the arrival counters of the current device

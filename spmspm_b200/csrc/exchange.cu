@@ -136,32 +136,6 @@ extern "C" int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compre
     a.split_k = Split_K;
     a.wait_flags = B_flags;
     a.wait_n = n_peers;
-    if (Split_K > 1) {
-        // fp16 partials into the workspace as usual (the SpMM kernel still waits for B's exchange); the
-        // reduction then stores the rows into the peers' buffers and writes the flags
-        spb::GatherOut g;
-        for (int q = 0; q < 8; ++q) {
-            g.outs[q] = q < n_peers ? C_peers[q] : nullptr;
-            g.flags[q] = q < n_peers ? flag_peers[q] : nullptr;
-            if (q < n_peers && (!C_peers[q] || !flag_peers[q] || (reinterpret_cast<uintptr_t>(C_peers[q]) & 15u))) {
-                spb::set_error("spb_spmm_bitmap_v3_allgather: peer %d: null or misaligned buffer", q);
-                return (int)cudaErrorInvalidValue;
-            }
-        }
-        g.n = n_peers;
-        g.flag_index = rank;
-        g.sequence = flag_peers[rank] + n_peers;
-        cudaError_t e = spb::exchange_counter((cudaStream_t)stream, &g.done);
-        if (e != cudaSuccess) return (int)e;
-        a.out = Reduction_Workspace;
-        e = spb::spmm_launch((cudaStream_t)stream, a);
-        if (e != cudaSuccess) return (int)e;
-        const size_t mn = (size_t)M_shard * N_Global;
-        const unsigned blocks = (unsigned)((mn / 8 + 255) / 256);
-        spb::splitk_reduce_gather_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(g, Reduction_Workspace, M_shard, mn,
-                                                                                 Split_K, M_full, row_offset);
-        return (int)cudaGetLastError();
-    }
     for (int q = 0; q < n_peers; ++q) {
         if (!C_peers[q] || !flag_peers[q] || (reinterpret_cast<uintptr_t>(C_peers[q]) & 15u)) {
             spb::set_error("spb_spmm_bitmap_v3_allgather: peer %d: null or misaligned buffer", q);
@@ -176,7 +150,30 @@ extern "C" int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compre
     a.row0 = row_offset;
     a.flag_index = rank;
     a.sequence = flag_peers[rank] + n_peers;  // this rank's own array is local memory
-    return (int)spb::spmm_launch((cudaStream_t)stream, a);
+    if (Split_K == 1) return (int)spb::spmm_launch((cudaStream_t)stream, a);
+    // Split_K > 1: fp16 partials into the workspace as usual (the SpMM kernel still waits for B's exchange).  When
+    // the kernel can fuse the reduction it also stores the rows into the peers' buffers and writes the flags;
+    // otherwise the reduction kernel below does.
+    bool fused = false;
+    a.out = Reduction_Workspace;
+    a.reduce_fused = &fused;
+    spb::GatherOut g;
+    for (int q = 0; q < 8; ++q) {
+        g.outs[q] = q < n_peers ? C_peers[q] : nullptr;
+        g.flags[q] = q < n_peers ? flag_peers[q] : nullptr;
+    }
+    g.n = n_peers;
+    g.flag_index = rank;
+    g.sequence = flag_peers[rank] + n_peers;
+    cudaError_t e = spb::exchange_counter((cudaStream_t)stream, &g.done);
+    if (e != cudaSuccess) return (int)e;
+    e = spb::spmm_launch((cudaStream_t)stream, a);
+    if (e != cudaSuccess || fused) return (int)e;
+    const size_t mn = (size_t)M_shard * N_Global;
+    const unsigned blocks = (unsigned)((mn / 8 + 255) / 256);
+    spb::splitk_reduce_gather_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(g, Reduction_Workspace, M_shard, mn, Split_K,
+                                                                             M_full, row_offset);
+    return (int)cudaGetLastError();
 }
 
 extern "C" int spb_wait_flags(void* stream, uint32_t* flags, int n_peers)

@@ -48,8 +48,13 @@ namespace spb {
 #if SPB_PROF
 __device__ unsigned long long g_prof[32];
 #define PROF_T(i) do { const uint32_t t_ = clock(); pacc[i] += t_ - plast; plast = t_; } while (0)
+// time line of a launch: earliest and latest %globaltimer (ns) over all CTAs at event i, in g_prof[32 + 2 * i], [33 + 2 * i]
+__device__ unsigned long long g_tl[32];
+#define PROF_EV(i) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+                        atomicMin(&g_tl[2 * (i)], t_); atomicMax(&g_tl[2 * (i) + 1], t_); } while (0)
 #else
 #define PROF_T(i) do {} while (0)
+#define PROF_EV(i) do {} while (0)
 #endif
 namespace {
 
@@ -121,6 +126,7 @@ struct KernelParams {
     float* partials;
     int* counters;
     int balanced, units;
+    int weights_ahead;  // 1: the weight-streaming warps do not wait for the stream's preceding kernel
     // Output: normally one buffer [N][M] (or the split-K partials).  For the fused all-gather the rows of this
     // launch go to rows row0.. of n_out buffers [N][ld_out], this GPU's and its peers' (peer memory mapped
     // into this process), and when the last CTA has finished, the launch's sequence number is written to
@@ -128,6 +134,13 @@ struct KernelParams {
     uint16_t* outs[kMaxPeers];
     uint32_t* flags[kMaxPeers];
     int n_out, ld_out, row0, n_flags, flag_index;
+    // Split-K under the static schedule with the reduction fused in: the fp16 partials go to outs[0] as usual; the
+    // CTAs of a row block count themselves on red_counters[activation tile * row_blocks + row block], and the
+    // one that completes the count sums the partials (fp32, in range order: the arithmetic of the separate
+    // reduction kernel) into rows red_row0.. of n_red buffers [N][red_ld].  red_counters == null: no fused reduction.
+    uint16_t* red_outs[kMaxPeers];
+    int* red_counters;
+    int n_red, red_ld, red_row0;
     uint32_t* sequence;  // this GPU's count of fused launches on these buffers
     int* done;           // CTAs of the launch that have finished
     // The activations of this launch are the result of an earlier exchange: its flag array on this GPU
@@ -484,30 +497,47 @@ __device__ __forceinline__ void lds64(uint32_t addr, uint32_t& a, uint32_t& b)
 // permute selectors that cut them out are computed from those counts.  The tables are kept to 32-bit
 // entries because the decode warps are bound by shared-memory wavefronts, not by arithmetic: a 4-byte load
 // from a 64-byte table is one conflict-free wavefront, an 8-byte one at least two.
-__device__ __forceinline__ uint32_t pair_sel_bottom(uint32_t lo, uint32_t hi)
+__host__ __device__ constexpr uint32_t pair_sel_bottom(uint32_t lo, uint32_t hi)
 {
     // window = {next value, the one after}; zero register in bytes 4..7
     const uint32_t p_lo = lo ? 0x10u : 0x54u;
     const uint32_t p_hi = hi ? (lo ? 0x32u : 0x10u) : 0x54u;
     return p_lo | (p_hi << 8);
 }
-__device__ __forceinline__ uint32_t pair_sel_top(uint32_t lo, uint32_t hi)
+__host__ __device__ constexpr uint32_t pair_sel_top(uint32_t lo, uint32_t hi)
 {
     // window = {second to last value, last value}
     const uint32_t p_hi = hi ? 0x32u : 0x54u;
     const uint32_t p_lo = lo ? (hi ? 0x10u : 0x32u) : 0x54u;
     return p_lo | (p_hi << 8);
 }
-__device__ __forceinline__ uint32_t lut_low_entry(uint32_t n)
+__host__ __device__ constexpr uint32_t lut_low_entry(uint32_t n)
 {
     const uint32_t b0 = n & 1, b1 = (n >> 1) & 1, b2 = (n >> 2) & 1, b3 = (n >> 3) & 1;
     return pair_sel_bottom(b0, b1) | (pair_sel_bottom(b2, b3) << 16);
 }
-__device__ __forceinline__ uint32_t lut_high_entry(uint32_t n)
+__host__ __device__ constexpr uint32_t lut_high_entry(uint32_t n)
 {
     const uint32_t b4 = n & 1, b5 = (n >> 1) & 1, b6 = (n >> 2) & 1, b7 = (n >> 3) & 1;
     return pair_sel_top(b6, b7) | (pair_sel_top(b4, b5) << 16);
 }
+
+// The selector table as it lies in shared memory: entry (mask g, copy c) at 8 * (16 * g + c) bytes, c = 0..15, so
+// that the 16 lanes of a half warp, each reading its own copy, always touch 16 different 8-byte bank pairs.
+// Built at compile time; every CTA fetches it with one bulk copy.
+struct SelectorTable {
+    uint32_t v[2 * 16 * 256];
+    constexpr SelectorTable() : v{}
+    {
+        for (uint32_t g = 0; g < 256; ++g)
+            for (uint32_t c = 0; c < 16; ++c) {
+                v[2 * (16 * g + c)] = lut_low_entry(g & 15u);
+                v[2 * (16 * g + c) + 1] = lut_high_entry(g >> 4);
+            }
+    }
+};
+static_assert(sizeof(SelectorTable) == kLutBytes, "selector table size");
+__device__ __align__(128) const SelectorTable g_selector_table = SelectorTable();
 
 // Expansion of one 8-element row segment (one row of one 8x8 tile) into 4 registers of packed fp16,
 // split into a load half and a compute half so that the loads of several segments can be in flight
@@ -566,6 +596,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t pad = (uint32_t)(smem - smem_raw);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) PROF_EV(0);
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     const uint32_t bar_full = smem_u32(bars);                         // [kMaxStages]
@@ -574,7 +605,8 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t bar_afree = bar_aready + 8 * kABlocks;             // [kABlocks]: ... read by its MMAs
     const uint32_t bar_accfull = bar_afree + 8 * kABlocks;            // [2]
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kABlocks + 4));
+    const uint32_t bar_lut = bar_accempty + 16;                       // the selector table has landed
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kABlocks + 5));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     volatile int* finisher = reinterpret_cast<volatile int*>(tmem_holder + 2);
     const uint32_t stage0 = smem_u32(smem + kHeaderBytes);
@@ -602,13 +634,13 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             mbar_init(bar_accfull + 8 * i, 1);
             mbar_init(bar_accempty + 8 * i, 4);
         }
+        mbar_init(bar_lut, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    for (uint32_t i = threadIdx.x; i < 256u * 16u; i += kThreads) {
-        const uint32_t g = i >> 4;
-        *reinterpret_cast<uint2*>(smem + 1024 + kTileTabBytes * 4 * kDecodeGroups + 8 * i) =
-            make_uint2(lut_low_entry(g & 15u), lut_high_entry(g >> 4));
+        // the selector table is the library's own constant data: it can be fetched before the preceding kernel of
+        // the stream has finished
+        mbar_expect_tx(bar_lut, (uint32_t)kLutBytes);
+        bulk_g2s(smem_u32(smem + 1024 + kTileTabBytes * 4 * kDecodeGroups), &g_selector_table, (uint32_t)kLutBytes, bar_lut);
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
@@ -622,30 +654,43 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t tmem_base = *tmem_holder;
     const uint32_t tmem_a0 = tmem_base + kAccCols;
 
-    // Everything above touches only this CTA's shared and tensor memory, so under programmatic dependent
-    // launch it overlaps the tail of the preceding kernel of the stream.  From here on global memory is
-    // read and written: wait until that kernel has completed and its writes are visible.  Kernels queued
-    // behind this one may be set up as soon as every CTA has passed this point.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Programmatic dependent launch.  Everything above touches only this CTA's shared and tensor memory, so it
+    // overlaps the tail of the preceding kernel of the stream.  From here on the roles differ in what they may
+    // do before that kernel has completed (griddepcontrol.wait):
+    //   - the warps that stream the weight (packed values, bitmaps, offsets, max_nnz_intile) do not wait at all.
+    //     The weight arrays are never written by this library's SpMM kernels, the only kernels that let a
+    //     dependent start before they have finished; any other kernel ahead in the stream has completed all
+    //     its thread blocks before this one starts.  So the ring of stages fills with weights while the
+    //     slowest CTAs of the preceding SpMM are still in their epilogue;
+    //   - the warp that loads the activation tiles, the epilogue warps (stores to C, to the partial sums, to
+    //     the peers; the scratch of the schedules) and everything that reads the exchange flags wait first.
+    // Kernels queued behind this one may be set up as soon as every CTA has passed this point.
+    if (threadIdx.x == 0) PROF_EV(1);
+    if (!p.weights_ahead) asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 0) PROF_EV(2);
 
     // ---- carve-up ------------------------------------------------------------------------
     // A stage holds kKT consecutive k-tiles of one 128-row block: the activation tiles, then for each
     // of the two 64-row global-tile rows one contiguous run of packed values, the bitmaps and the
     // median offsets, then the start of every global tile's values inside its run.
-    int max_nnz = *p.max_nnz;
-    if (max_nnz < 8) max_nnz = 8;
-    if (max_nnz > 4096) max_nnz = 4096;
-    const uint32_t vmax = ((uint32_t)max_nnz * 2 + 127) & ~127u;  // bytes per global tile, upper bound
+    // The stage size depends on max_nnz_intile, a load from global memory that takes most of a microsecond.  The
+    // load is issued here; what is derived from it (SPB_CARVE) is computed by each role only after the part of
+    // its start-up that does not need it (walking to its first work item, fetching the first tile offsets), so
+    // that nobody sits on the load.
+    int max_nnz_ld;
+    asm volatile("ld.global.cg.s32 %0, [%1];" : "=r"(max_nnz_ld) : "l"(p.max_nnz));
     constexpr uint32_t kBTile = NPAD * 128;
-    const uint32_t off_v0 = kKT * kBTile, off_v1 = off_v0 + kKT * vmax;
-    const uint32_t off_bm0 = off_v1 + kKT * vmax, off_bm1 = off_bm0 + kKT * 512;
-    const uint32_t off_mt0 = off_bm1 + kKT * 512, off_mt1 = off_mt0 + kKT * 16;
-    const uint32_t off_rel = off_mt1 + kKT * 16;  // [2][kKT] uint32: byte offset of a tile's values in its run
-    const uint32_t stage_bytes = (off_rel + 8 * kKT + 1023) & ~1023u;
-    const uint32_t avail = p.smem_bytes - pad - kHeaderBytes;
-    int S = (int)(avail / stage_bytes);
-    if (S > kMaxStages) S = kMaxStages;
+#define SPB_CARVE()                                                                                                   \
+    const int max_nnz = max_nnz_ld < 8 ? 8 : max_nnz_ld > 4096 ? 4096 : max_nnz_ld;                                   \
+    const uint32_t vmax = ((uint32_t)max_nnz * 2 + 127) & ~127u; /* bytes per global tile, upper bound */             \
+    const uint32_t off_v0 = kKT * kBTile, off_v1 = off_v0 + kKT * vmax;                                               \
+    const uint32_t off_bm0 = off_v1 + kKT * vmax, off_bm1 = off_bm0 + kKT * 512;                                      \
+    const uint32_t off_mt0 = off_bm1 + kKT * 512, off_mt1 = off_mt0 + kKT * 16;                                       \
+    const uint32_t off_rel = off_mt1 + kKT * 16; /* [2][kKT] uint32: byte offset of a tile's values in its run */     \
+    const uint32_t stage_bytes = (off_rel + 8 * kKT + 1023) & ~1023u;                                                 \
+    const int S = min((int)((p.smem_bytes - pad - kHeaderBytes) / stage_bytes), kMaxStages);                          \
+    (void)off_v0; (void)off_bm0; (void)off_bm1; (void)off_mt0; (void)off_mt1; (void)off_rel; (void)S; (void)vmax; (void)off_v1
 
 
     // The A operands of two stages live in TMEM (buffer = stage parity), one 32-column block per k-tile.
@@ -653,8 +698,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     // and afree (the MMAs that read it have completed), so that a decode group only ever waits for the
     // tensor core's work on its own k-tiles, never for another group.  Which phase of a block's barriers
     // comes next is kept as one bit per block (ph) by everybody who walks the stage sequence.
-    // (Nothing above this line needs the stage size, which depends on max_nnz_intile, a load from global
-    // memory: the producers below start fetching the tile offsets before they look at it.)
     if (warp < kEpilogueWarp0) {
         if constexpr (kResize) reg_dealloc<kRegsControl>();
         if (warp != kMmaWarp) {
@@ -692,8 +735,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 if (prole != 0 || !b.c.valid) return;
                 const size_t g = (size_t)(2 * b.c.w.y) * p.kt_total + b.c.w.k0 + b.base;
                 if (lane <= b.c.w.nk - b.base) {
-                    b.v0 = __ldg(p.gtile + g + lane);
-                    if ((2 * b.c.w.y + 1) < p.gm_total) b.v1 = __ldg(p.gtile + g + p.kt_total + lane);
+                    // (through L2 only: with the launch overlap above, a line of this SM's L1 could predate the
+                    // kernel that wrote the array)
+                    b.v0 = __ldcg(p.gtile + g + lane);
+                    if ((2 * b.c.w.y + 1) < p.gm_total) b.v1 = __ldcg(p.gtile + g + p.kt_total + lane);
                 }
             };
             auto batch_after = [&](const Batch& b) -> Batch {
@@ -719,6 +764,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             load_batch(cur);
             Batch nxt = batch_after(cur);
             load_batch(nxt);
+            SPB_CARVE();
 #if SPB_PROF
             uint32_t pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, plast = clock();
 #endif
@@ -729,6 +775,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 *abort_flag = 1;
                 ok = false;
             }
+            if (prole == 2) asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations come from the preceding kernel
             if (kExchange && ok && prole == 2 && p.wait_flags && st.valid) {
                 // the activations come out of an exchange between the GPUs: bounded wait for every rank's rows
                 bool here = lane >= p.wait_n;
@@ -830,6 +877,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 }
                 PROF_T(2);
 #if SPB_PROF
+                if (pacc[7] == 0 && prole == 0 && lane == 0) PROF_EV(3);
                 ++pacc[7];
 #endif
             }
@@ -853,6 +901,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             Walk wk;
             wk.template init<kBalanced>(p);
             Item w;
+            SPB_CARVE();
 #if SPB_PROF
             uint32_t pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, plast = clock();
 #endif
@@ -885,6 +934,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         }
                         __syncwarp();
                         PROF_T(2);
+#if SPB_PROF
+                        if (pacc[6] == 0 && lane == 0) { PROF_EV(5); pacc[6] = 1; }
+#endif
                     }
                     ph ^= block_mask(tb, nv);
                     tb = (tb + (uint32_t)nv) % kABlocks;
@@ -894,6 +946,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 __syncwarp();
                 ++idx;
             }
+            if (lane == 0) PROF_EV(6);
 #if SPB_PROF
             if (lane == 0)
                 for (int i = 0; i < 3; ++i) atomicAdd(&g_prof[8 + i], (unsigned long long)pacc[i]);
@@ -902,6 +955,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     } else if (warp < kDecodeWarp0) {
         if constexpr (kResize) reg_dealloc<kRegsEpilogue>();
         // ================================================================= epilogue
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // before the first access to C, the scratch or the flags
         const int quad = warp & 3;
         const int row_in_block = quad * 32 + lane;
         uint32_t idx = 0;
@@ -918,6 +972,53 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             if (p.n_flags > 0) my_seq = *reinterpret_cast<volatile uint32_t*>(p.sequence) + 1u;
             if (p.wait_flags) consumed = *reinterpret_cast<volatile uint32_t*>(p.wait_flags + p.wait_n + 1) + 1u;
         }
+        // Fused split-K reduction (static schedule): called by the four epilogue warps after they have stored their
+        // item's fp16 partial.  One thread publishes the CTA's stores and counts the CTA on the row block's counter;
+        // the CTA that completes the count re-reads all Split_K partials of its 128 x NPAD block (they sit in L2) and
+        // writes the sums: 8 consecutive rows per thread with 16-byte accesses, fp32 sums in range order, one
+        // rounding, exactly what splitk_reduce_kernel computes.
+        auto reduce_if_last = [&](const Item& it) {
+            bar_sync_epilogue();
+            if (leader) {
+                // one acquire-release atomic: it publishes the CTA's partial (the barrier ordered the other
+                // threads' stores before it) and, for the CTA that completes the count, makes the others' visible
+                int* cnt = p.red_counters + it.nt * p.row_blocks + it.y;
+                int before;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(before) : "l"(cnt) : "memory");
+                const bool last = before == p.split_k - 1;
+                if (last) *cnt = 0;  // ready for the next launch
+                *finisher = last;
+            }
+            bar_sync_epilogue();
+            if (!*finisher) return;
+            const int t = (warp - kEpilogueWarp0) * 32 + lane;
+            const int rowg = it.y * 128 + (t & 15) * 8;
+            if (rowg >= p.M) return;
+            const size_t mn = (size_t)p.M * p.N;
+            const int col_end = min(p.N, (it.nt + 1) * NPAD);
+            for (int col = it.nt * NPAD + (t >> 4); col < col_end; col += 8) {
+                const uint16_t* src = p.outs[0] + (size_t)col * p.M + rowg;
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                for (int s2 = 0; s2 < p.split_k; ++s2) {
+                    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)s2 * mn));
+                    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(h[j]);
+                        acc[2 * j] += f.x;
+                        acc[2 * j + 1] += f.y;
+                    }
+                }
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+                const size_t at = (size_t)col * p.red_ld + (size_t)p.red_row0 + rowg;
+                for (int q = 0; q < p.n_red; ++q) *reinterpret_cast<uint4*>(p.red_outs[q] + at) = o;
+            }
+        };
         while (ok && wk.template next<kBalanced>(p, w)) {
             const int grow = w.y * 128 + row_in_block;
             // element (col, grow) of this launch's result, in every output buffer
@@ -932,6 +1033,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     const int col = w.nt * NPAD + n;
                     if (col < p.N && grow < p.M) store(col, (uint16_t)0);
                 }
+                if (!kBalanced && p.red_counters) reduce_if_last(w);
                 continue;
             }
             // A run that is only part of its range: the CTAs that share the range (c_first..c_last, in k
@@ -1087,8 +1189,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     if (leader) p.counters[w.id] = 0;
                 }
             }
+            if (!kBalanced && p.red_counters) reduce_if_last(w);
             ++idx;
         }
+        if (leader) PROF_EV(7);
         if (kExchange && p.done) {
             // Fused all-gather: every thread's stores to the peers are made visible system-wide before the CTA
             // counts itself as finished; the CTA that completes the count numbers the launch and tells the peers.
@@ -1124,6 +1228,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         const int row = quad * 32 + lane;      // weight row inside the 128-row block
         const int chunk = row >> 6, rr = row & 63;   // 64-row global-tile row of the block, row inside it
         const int r_in_tile = rr & 7;
+        SPB_CARVE();
         const uint32_t my_v = chunk ? off_v1 : off_v0;
         const uint32_t rel0 = off_rel + 4 * (uint32_t)(chunk * kKT);
         // Lane l looks after tile l & 15 of median tile 2 * (quad & 1) + (l >> 4) of each k-tile of the unit.
@@ -1142,6 +1247,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         Walk wk;
         wk.template init<kBalanced>(p);
         Item w;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_lut, 0, abort_flag));  // the selector table
 #if SPB_PROF
         uint32_t pacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, plast = clock();
 #endif
@@ -1159,6 +1265,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 PROF_T(1);
+#if SPB_PROF
+                if (dw == 0 && lane == 0 && pacc[7] == 0 && plast != 0xffffffffu) { PROF_EV(4); }
+#endif
                 if (usub < nun) {
                     const int sub0 = usub * kUnit, nk = min(kUnit, nv - sub0);  // the unit's k-tiles of the stage
                     const uint32_t st = stage0 + slot * stage_bytes;
@@ -1261,6 +1370,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             atomicOr(p.status, (int)kStatusWaitTimeout);
             // give copies that may still be in flight a bounded chance to land before the CTA's
             // shared memory is released
+            SPB_CARVE();
+            for (uint32_t spin = 0; spin < 4096; ++spin)
+                if (mbar_try(bar_lut, 0)) break;
             for (int i = 0; i < S; ++i)
                 for (uint32_t spin = 0; spin < 4096; ++spin)
                     if (mbar_try(bar_full + 8 * i, 0) || mbar_try(bar_full + 8 * i, 1)) break;
@@ -1270,6 +1382,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
+    if (threadIdx.x == 0) PROF_EV(8);
 }
 
 // ------------------------------------------------------------------------------ host side
@@ -1328,6 +1441,7 @@ struct ScratchSet {
 };
 std::mutex g_scratch_mu;
 ScratchSet g_scratch[64][kScratchSets];
+std::atomic<int> g_weights_ahead{1};  // see spb_set_weight_prefetch
 std::atomic<int> g_schedule{0};       // 0: by the cost model, 1: always static, 2: balanced whenever possible
 thread_local int t_static_depth = 0;  // > 0: this thread's calls use the static schedule
 
@@ -1479,21 +1593,33 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     p.counters = nullptr;
     p.balanced = 0;
     p.units = 0;
-    const bool fused = a.n_out > 0;
+    // Where the result goes.  Split_K == 1: straight to the final destination, C or (fused all-gather) the peers'
+    // buffers.  Split_K > 1: fp16 partials to the workspace (a.out); the final destination is written by the
+    // fused reduction when that is possible (decided below), else by the caller's reduction launch.
+    const bool split = a.split_k > 1;
+    const bool gather = a.n_out > 0;
+    const bool direct_gather = gather && !split;
     for (int q = 0; q < kMaxPeers; ++q) {
-        p.outs[q] = fused && q < a.n_out ? a.outs[q] : nullptr;
-        p.flags[q] = fused && q < a.n_flags ? a.flags[q] : nullptr;
+        p.outs[q] = direct_gather && q < a.n_out ? a.outs[q] : nullptr;
+        p.flags[q] = nullptr;
+        p.red_outs[q] = nullptr;
     }
-    if (!fused) p.outs[0] = a.out;
-    p.n_out = fused ? a.n_out : 1;
-    p.ld_out = fused ? a.ld_out : a.M;
-    p.row0 = fused ? a.row0 : 0;
-    p.n_flags = fused ? a.n_flags : 0;
+    if (!direct_gather) p.outs[0] = a.out;
+    p.n_out = direct_gather ? a.n_out : 1;
+    p.ld_out = direct_gather ? a.ld_out : a.M;
+    p.row0 = direct_gather ? a.row0 : 0;
+    p.n_flags = 0;
+    p.red_counters = nullptr;
+    p.n_red = 0;
+    p.red_ld = 0;
+    p.red_row0 = 0;
+    if (a.reduce_fused) *a.reduce_fused = false;
     p.flag_index = a.flag_index;
     p.sequence = a.sequence;
     p.done = nullptr;
     p.wait_flags = a.wait_flags;
     p.wait_n = a.wait_n;
+    p.weights_ahead = g_weights_ahead.load();
     const int mode = g_schedule.load();
     if (mode != 1 && t_static_depth == 0 && (units + 1) * di.sms < (1LL << 31) && p.num_items <= kCounterCap &&
         no_empty_range && (mode == 2 || prefer_balanced(p.row_blocks, p.n_tiles, p.kt_total, a.split_k, di.sms, NPAD))) {
@@ -1505,6 +1631,25 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
             p.units = (int)units;
         }
     }
+    // Fused split-K reduction: static schedule, a final destination, the stream's counters (spb_init)
+    bool red_fused = false;
+    if (split && !p.balanced && t_static_depth == 0 && (gather || a.final_out) && p.n_tiles * p.row_blocks <= kCounterCap &&
+        ((size_t)a.M * a.N) % 8 == 0) {
+        if (const ScratchSet* sc = scratch_for(s, dev, di.sms, false)) {
+            p.red_counters = sc->counters;
+            p.n_red = gather ? a.n_out : 1;
+            for (int q = 0; q < p.n_red; ++q) p.red_outs[q] = gather ? a.outs[q] : a.final_out;
+            p.red_ld = gather ? a.ld_out : a.M;
+            p.red_row0 = gather ? a.row0 : 0;
+            red_fused = true;
+            if (a.reduce_fused) *a.reduce_fused = true;
+        }
+    }
+    // the kernel tells the peers itself when it also writes the final rows
+    if (gather && (!split || red_fused)) {
+        p.n_flags = a.n_flags;
+        for (int q = 0; q < kMaxPeers; ++q) p.flags[q] = q < a.n_flags ? a.flags[q] : nullptr;
+    }
     if (p.n_flags > 0 || p.wait_flags) {
         // the count of finished CTAs lives behind the arrival counters of the stream's scratch
         const ScratchSet* sc = scratch_for(s, dev, di.sms, false);
@@ -1515,7 +1660,7 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
         p.done = sc->counters + kCounterCap;
     }
 
-    const bool exchange = fused || p.wait_flags != nullptr;
+    const bool exchange = gather || p.wait_flags != nullptr;
     const int variant = (exchange ? 2 : 0) + (p.balanced ? 1 : 0);
     auto kernel = variant == 3   ? spmm_bitmap_tcgen05_kernel<NPAD, true, true>
                   : variant == 2 ? spmm_bitmap_tcgen05_kernel<NPAD, true, false>
@@ -1563,9 +1708,12 @@ cudaError_t exchange_counter(cudaStream_t s, int** out)
 extern "C" int spb_debug_prof(unsigned long long* out, int clear)
 {
     cudaError_t e = cudaMemcpyFromSymbol(out, spb::g_prof, sizeof(unsigned long long) * 32);
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 32, spb::g_tl, sizeof(unsigned long long) * 32);
     if (e == cudaSuccess && clear) {
-        unsigned long long z[32] = {};
+        unsigned long long z[32] = {}, t[32];
+        for (int i = 0; i < 32; ++i) t[i] = (i & 1) ? 0ull : ~0ull;
         e = cudaMemcpyToSymbol(spb::g_prof, z, sizeof(z));
+        if (e == cudaSuccess) e = cudaMemcpyToSymbol(spb::g_tl, t, sizeof(t));
     }
     return (int)e;
 }
@@ -1596,6 +1744,8 @@ cudaError_t init_stream(cudaStream_t s)
     }
     return cudaSuccess;
 }
+
+int set_weight_prefetch(int on) { return g_weights_ahead.exchange(on ? 1 : 0); }
 
 int set_schedule(int mode)
 {
