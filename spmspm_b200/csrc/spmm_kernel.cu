@@ -606,7 +606,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     const uint32_t bar_accfull = bar_afree + 8 * kABlocks;            // [2]
     const uint32_t bar_accempty = bar_accfull + 16;                   // [2]
     const uint32_t bar_lut = bar_accempty + 16;                       // the selector table has landed
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (2 * kMaxStages + 2 * kABlocks + 5));
+    const uint32_t bar_b = bar_lut + 8;                               // [kMaxStages]: a stage's activation tiles have landed
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + 8 * (3 * kMaxStages + 2 * kABlocks + 5));
+    static_assert(8 * (3 * kMaxStages + 2 * kABlocks + 5) + 16 <= 1024, "barriers and flags fit the first KB of the header");
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     volatile int* finisher = reinterpret_cast<volatile int*>(tmem_holder + 2);
     const uint32_t stage0 = smem_u32(smem + kHeaderBytes);
@@ -624,6 +626,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     if (threadIdx.x == 0) {
         for (int i = 0; i < kMaxStages; ++i) {
             mbar_init(bar_full + 8 * i, 1);
+            // The activation tiles complete on a barrier of their own, which only the MMA warp waits on: the
+            // decode warps can then expand the weights of a stage (all the full barrier covers) before the
+            // activations exist, i.e. while the stream's preceding kernel is still running.
+            mbar_init(bar_b + 8 * i, 1);
             mbar_init(bar_empty + 8 * i, 4 * kDecodeGroups + 1);  // every decode warp + the MMA commit
         }
         for (int i = 0; i < kABlocks; ++i) {
@@ -852,8 +858,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 // one elected lane issues this warp's copies with warp-uniform operands
                 if (elect_one()) {
                     if (prole == 0) {
-                        const uint32_t tx =
-                            (uint32_t)nv * kBTile + n0 + n1 + (chunk1 ? 2u : 1u) * (uint32_t)nv * (512u + 16u);
+                        const uint32_t tx = n0 + n1 + (chunk1 ? 2u : 1u) * (uint32_t)nv * (512u + 16u);
                         mbar_expect_tx(full, tx);
                         if (n0) bulk_g2s(sbase + off_v0, p.vals + a0, n0, full);
                         if (n1) bulk_g2s(sbase + off_v1, p.vals + a1, n1, full);
@@ -865,9 +870,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                             bulk_g2s(sbase + off_mt1, p.mtile + (g0 + p.kt_total) * 4, (uint32_t)nv * 16u, full);
                         }
                     } else {
+                        mbar_expect_tx(bar_b + 8 * slot, (uint32_t)nv * kBTile);
                         for (int j = 0; j < nv; ++j)  // activation tile of k-tile j
                             tma_load_2d(sbase + (uint32_t)j * kBTile, &tmap_b, (cw.k0 + ckk0 + j) * 64, cw.nt * NPAD,
-                                        full);
+                                        bar_b + 8 * slot);
                     }
                 }
                 __syncwarp();
@@ -896,7 +902,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             // the decode groups that the block may be rewritten; the last one of a stage also arrives on
             // the stage's empty barrier, for the producers.
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            uint32_t idx = 0, slot = 0, tb = 0, ph = 0;  // tb: block of the stage's first k-tile
+            uint32_t idx = 0, slot = 0, sround = 0, tb = 0, ph = 0;  // tb: block of the stage's first k-tile
             bool ok = true;
             Walk wk;
             wk.template init<kBalanced>(p);
@@ -915,6 +921,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 for (int kk0 = 0; kk0 < w.nk && ok; kk0 += kKT) {
                     const int nv = min(kKT, w.nk - kk0);
                     const uint32_t sbase = stage0 + slot * stage_bytes;
+                    ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_b + 8 * slot, sround & 1u, abort_flag));  // activation tiles
                     for (int sub = 0; sub < nv && ok; ++sub) {
                         const uint32_t blk = (tb + (uint32_t)sub) % kABlocks;
                         PROF_T(0);
@@ -940,7 +947,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     }
                     ph ^= block_mask(tb, nv);
                     tb = (tb + (uint32_t)nv) % kABlocks;
-                    if (++slot == (uint32_t)S) slot = 0;
+                    if (++slot == (uint32_t)S) {
+                        slot = 0;
+                        ++sround;
+                    }
                 }
                 if (ok && elect_one()) tc_commit(bar_accfull + 8 * accbuf);
                 __syncwarp();
@@ -1375,7 +1385,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 if (mbar_try(bar_lut, 0)) break;
             for (int i = 0; i < S; ++i)
                 for (uint32_t spin = 0; spin < 4096; ++spin)
-                    if (mbar_try(bar_full + 8 * i, 0) || mbar_try(bar_full + 8 * i, 1)) break;
+                    if ((mbar_try(bar_full + 8 * i, 0) || mbar_try(bar_full + 8 * i, 1)) &&
+                        (mbar_try(bar_b + 8 * i, 0) || mbar_try(bar_b + 8 * i, 1)))
+                        break;
         }
         __syncthreads();
     }
