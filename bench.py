@@ -33,6 +33,9 @@ WORKLOADS = {
     "opt13b_layer_set_s60": {"shapes": [(15360, 5120), (5120, 5120), (20480, 5120), (5120, 20480)], "ns": [8, 16, 32],
                              "sparsity": 0.6},
     "opt66b_tp": {"shapes": [(27648, 9216), (9216, 9216), (36864, 9216), (9216, 36864)], "ns": [16], "sparsity": 0.6},
+    # one synthetic OPT-66B decoder layer, tensor-parallel as FasterTransformer splits it (see spmspm_b200/layer.py);
+    # handled by run_layer, the shapes here are only what the JSON line reports
+    "opt66b_layer": {"shapes": [(27648, 9216), (9216, 9216), (36864, 9216), (9216, 36864)], "ns": [8, 512], "sparsity": 0.6},
 }
 WORKLOAD = "opt13b_layer_set_s60"
 SHAPES = WORKLOADS[WORKLOAD]["shapes"]
@@ -207,7 +210,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="opt13b_layer_set_s60", choices=sorted(WORKLOADS),
                     help="opt13b_layer_set_s60: the headline set; opt66b_tp: the OPT-66B shapes at N = 16 with every "
-                         "row shard's encoding checked against the CPU encoder inside the run")
+                         "row shard's encoding checked against the CPU encoder inside the run; opt66b_layer: one "
+                         "synthetic OPT-66B decoder layer, batch 8, 64 prompt tokens, 128 generated tokens, tokens/s")
     ap.add_argument("--case", default=None,
                     help="M,K,N[,sparsity[,split_k]]: time one SpMM shape instead of a set "
                          "(used for per-shape tables and for small profiler captures)")
@@ -254,6 +258,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     l2_bytes = int(torch.cuda.get_device_properties(dev).L2_cache_size)
+    if args.workload == "opt66b_layer" and not args.case:
+        run_layer(args, sp, dist, dev, rank, world, local_rank)
+        return
 
     # ---- weights: generate, encode on the GPU, keep only this rank's row shard
     mats = []
@@ -516,6 +523,46 @@ def main():
         finish_ranks(dist, 1 if failed else 0)
     if failed:
         sys.exit(1)
+
+
+def run_layer(args, sp, dist, dev, rank, world, local_rank):
+    """One synthetic OPT-66B decoder layer (hidden 9216, 72 heads, FFN 36864, 60 % pruned), batch 8: a prompt of 64
+    tokens per sequence, then 128 generated tokens; QKV and FC1 split by rows, out-proj and FC2 by columns with an
+    all-reduce (one-shot over peer stores, or NCCL).  A step is one whole generation.  tokens/s as the reference's
+    plots compute it (end2end_inference/draw_plot.py:120-123): batch * generated tokens / latency, per layer."""
+    from spmspm_b200.layer import SparseOptDecoderLayer, generate_timed
+    hidden, heads, ffn, batch, prompt, new = 9216, 72, 36864, 8, 64, 128
+    results = {}
+    kinds = ["none"] if world == 1 else (["peer", "nccl"] if args.exchange == "auto" else [args.exchange])
+    for kind in kinds:
+        try:
+            layer = SparseOptDecoderLayer(hidden, heads, ffn, SPARSITY, dev, batch=batch, max_len=prompt + new, reduce=kind)
+        except Exception as exc:
+            if rank == 0:
+                print(f"[bench] layer with reduce={kind} unavailable ({type(exc).__name__}: {exc})", file=sys.stderr)
+            continue
+        with ClockSampler(local_rank) as clocks:
+            total, pre, per_step, graphed = generate_timed(layer, prompt, new, steps=max(args.steps // 4, 2), warmup=2)
+        results[kind] = {"s_per_generation": total, "prefill_ms": pre * 1e3, "decode_step_us": per_step * 1e6,
+                         "decode_graph": graphed, "tokens_per_s": batch * new / total, "clocks": clocks.summary(),
+                         "device_status": sp.device_status()}
+        del layer
+        torch.cuda.empty_cache()
+    if rank == 0:
+        best = max(results, key=lambda k: results[k]["tokens_per_s"])
+        r = results[best]
+        line = {"metric": "decoder_layer_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s (one layer)",
+                "n_gpus": world, "steps": max(args.steps // 4, 2), "warmup": 2, "ms_per_step": r["s_per_generation"] * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": "opt66b_layer", "hidden": hidden, "heads": heads, "ffn": ffn, "sparsity": SPARSITY,
+                           "batch": batch, "prompt_tokens": prompt, "generated_tokens": new,
+                           "parallelism": f"tp{world}_ft_split_allreduce_{best}" if world > 1 else "single_gpu"},
+                "tokens_per_s_per_gpu": r["tokens_per_s"] / world,
+                "tokens_per_s_64_layers": r["tokens_per_s"] / 64.0,
+                "by_reduce": results, "clocks": r["clocks"], "device_status": r["device_status"]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        finish_ranks(dist, 0)
 
 
 def finish_ranks(dist, code=0):

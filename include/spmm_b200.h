@@ -232,6 +232,27 @@ int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compressed_A, con
 int spb_wait_flags(void* stream, uint32_t* flags, int n_peers);
 
 /*
+ * K-split of tensor parallelism with a one-shot all-reduce over peer stores (no counterpart in the reference, whose
+ * caller runs an NCCL all-reduce after the out-proj and FC2 GEMMs; per-rank shapes in
+ * end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:284-285).  This rank holds the columns
+ * [rank*K/n, (rank+1)*K/n) of the weight (K_shard of them, encoded as a matrix of its own) and the matching slice
+ * of the activations B [N][K_shard].  part_peers[q] is rank q's buffer of n_peers partial results
+ * [n_peers][N_Global][M_Global] (fp16) as mapped into this process; this rank's product goes to slot `rank` of all of
+ * them, and entry `rank` of every flag array (n_peers + 2 uint32, zero before the first use) receives this rank's
+ * launch count, exactly as in spb_spmm_bitmap_v3_allgather, whose rules on call sequence, buffer reuse, B_flags and
+ * Split_K apply.  spb_allreduce_finish then waits (bounded; on expiry the device status word is set) for all ranks'
+ * partials in this rank's own buffer and writes C = fp16(sum over ranks in rank order of float(partial)) with the
+ * split-K reduction's arithmetic.  Peer memory is only ever written.  Needs spb_init on the calling stream.
+ */
+int spb_spmm_bitmap_v3_allreduce(void* stream, const uint16_t* Compressed_A, const int* TileOffsets,
+                                 const int* TileOffsets_Median, const uint64_t* bitmap, const int* max_nnz_intile,
+                                 const uint16_t* B, uint16_t* const* part_peers, uint32_t* const* flag_peers, int n_peers,
+                                 int rank, int M_Global, int N_Global, int K_shard, uint32_t* B_flags,
+                                 uint16_t* Reduction_Workspace, int Split_K);
+int spb_allreduce_finish(void* stream, uint16_t* C, const uint16_t* parts_local, uint32_t* flags_local, int n_peers,
+                         int M_Global, int N_Global);
+
+/*
  * Status word of the current device: 0 when no kernel of this library has hit a
  * bounded wait that ran out or an inconsistent offset since the last reset.
  * Synchronises the device.  spb_reset_device_status clears it.

@@ -363,6 +363,33 @@ def spmm_allgather(W: BitmapMatrix, B, C_peers, flag_peers, n_peers, rank, M_ful
     _check(code, "spb_spmm_bitmap_v3_allgather")
 
 
+def spmm_allreduce(W: BitmapMatrix, B, part_peers, flag_peers, n_peers, rank, B_flags=None, split_k=1, workspace=None,
+                   stream=None):
+    """spb_spmm_bitmap_v3_allreduce: SpMM of a column shard whose partial result goes to slot `rank` of every rank's
+    buffer (see spmspm_b200.dist.PeerReduce)."""
+    if not (B.is_cuda and B.dtype == torch.float16 and B.dim() == 2 and B.is_contiguous() and B.shape[1] == W.K):
+        raise SpmmError("B must be a contiguous CUDA float16 [N,K_shard] tensor")
+    if split_k > 1 and workspace is None:
+        workspace = torch.empty(split_k * B.shape[0] * W.M, dtype=torch.float16, device=B.device)
+    with torch.cuda.device(B.device):
+        _init_if_possible(stream)
+        code = _lib.load().spb_spmm_bitmap_v3_allreduce(_stream_ptr(stream), _ptr(W.vals), _ptr(W.gtile), _ptr(W.mtile),
+                                                        _ptr(W.bitmap), _ptr(W.max_nnz), _ptr(B), part_peers, flag_peers,
+                                                        n_peers, rank, W.M, B.shape[0], W.K, _ptr(B_flags),
+                                                        _ptr(workspace), split_k)
+    _check(code, "spb_spmm_bitmap_v3_allreduce")
+
+
+def allreduce_finish(out, parts_local, flags_local, n_peers, stream=None):
+    """spb_allreduce_finish: bounded wait for all ranks' partials, then their fp32 sum in rank order, rounded once."""
+    N, M = out.shape
+    with torch.cuda.device(out.device):
+        code = _lib.load().spb_allreduce_finish(_stream_ptr(stream), _ptr(out), _ptr(parts_local), _ptr(flags_local), n_peers,
+                                                M, N)
+    _check(code, "spb_allreduce_finish")
+    return out
+
+
 def wait_flags(flags, n_peers, stream=None):
     """spb_wait_flags: bounded device-side wait until every rank's rows of the current exchange have arrived."""
     with torch.cuda.device(flags.device):

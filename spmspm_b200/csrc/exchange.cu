@@ -187,3 +187,44 @@ extern "C" int spb_wait_flags(void* stream, uint32_t* flags, int n_peers)
     if (e != cudaSuccess) return (int)e;
     return (int)spb::wait_flags_launch((cudaStream_t)stream, flags, n_peers, status);
 }
+
+// K-split of tensor-parallel inference (out-proj and FC2 in FasterTransformer: every rank holds a slice of the
+// weight's columns and the matching slice of the activations, the partial products are summed over the ranks).
+// One-shot all-reduce over peer stores: this rank's SpMM writes its fp16 partial [N][M] into slot `rank` of every
+// rank's [n_peers][N][M] buffer (the fused all-gather above with the slot as the destination), and every rank then
+// sums the n_peers slots of its own buffer.  Nothing is ever loaded from a peer.
+extern "C" int spb_spmm_bitmap_v3_allreduce(void* stream, const uint16_t* Compressed_A, const int* TileOffsets,
+                                            const int* TileOffsets_Median, const uint64_t* bitmap,
+                                            const int* max_nnz_intile, const uint16_t* B, uint16_t* const* part_peers,
+                                            uint32_t* const* flag_peers, int n_peers, int rank, int M_Global,
+                                            int N_Global, int K_shard, uint32_t* B_flags, uint16_t* Reduction_Workspace,
+                                            int Split_K)
+{
+    if (n_peers < 1 || n_peers > 8 || rank < 0 || rank >= n_peers || !part_peers || !flag_peers || M_Global <= 0 ||
+        N_Global <= 0) {
+        spb::set_error("spb_spmm_bitmap_v3_allreduce: 1..8 peers, rank inside, pointer tables and positive sizes required");
+        return (int)cudaErrorInvalidValue;
+    }
+    uint16_t* slots[8];
+    for (int q = 0; q < n_peers; ++q) {
+        if (!part_peers[q]) {
+            spb::set_error("spb_spmm_bitmap_v3_allreduce: peer %d: null buffer", q);
+            return (int)cudaErrorInvalidValue;
+        }
+        slots[q] = part_peers[q] + (size_t)rank * M_Global * N_Global;
+    }
+    return spb_spmm_bitmap_v3_allgather(stream, Compressed_A, TileOffsets, TileOffsets_Median, bitmap, max_nnz_intile, B,
+                                        slots, flag_peers, n_peers, rank, M_Global, N_Global, K_shard, M_Global, 0,
+                                        B_flags, Reduction_Workspace, Split_K);
+}
+
+// Second half of the all-reduce: waits (bounded) until every rank's partial of the current exchange has arrived
+// in this rank's buffer, then C = fp16(sum over the ranks, in rank order, of float(partial)), the arithmetic of
+// the split-K reduction.
+extern "C" int spb_allreduce_finish(void* stream, uint16_t* C, const uint16_t* parts_local, uint32_t* flags_local,
+                                    int n_peers, int M_Global, int N_Global)
+{
+    int rc = spb_wait_flags(stream, flags_local, n_peers);
+    if (rc != 0) return rc;
+    return spb_splitk_reduce(stream, C, parts_local, M_Global, N_Global, n_peers);
+}

@@ -119,3 +119,58 @@ class PeerGather:
         api.wait_flags(self.flags[slot], self.world, stream=stream)
         self._turn += 1
         return self.bufs[slot]
+
+
+class PeerReduce:
+    """Partial-result buffers for the K-split SpMM with the one-shot all-reduce over peer stores
+    (spb_spmm_bitmap_v3_allreduce / spb_allreduce_finish).
+
+    Every rank allocates `slots` buffers [world, N, M] and a flag array per buffer in symmetric memory.
+    `spmm(W_local, B_local)` makes this rank's SpMM (its column shard of the weight times its slice of the
+    activations) store its fp16 partial into slot `rank` of every rank's current buffer; `reduce()` enqueues the
+    bounded wait for all ranks' partials and their sum (fp32, rank order, one rounding) and returns the [N, M]
+    result.  Calls alternate between the buffers; every rank must make the same sequence of calls.
+    """
+
+    def __init__(self, N, M, device, group=None, slots=2):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("PeerReduce serves up to 8 ranks")
+        self.N, self.M = N, M
+        self.bufs, self.flags, self._pptrs, self._fptrs, self.outs = [], [], [], [], []
+        for _ in range(slots):
+            buf = symm_mem.empty((self.world, N, M), dtype=torch.float16, device=device)
+            flg = symm_mem.empty((self.world + 2,), dtype=torch.int32, device=device)
+            buf.zero_()
+            flg.zero_()
+            hb = symm_mem.rendezvous(buf, self.group.group_name)
+            hf = symm_mem.rendezvous(flg, self.group.group_name)
+            self.bufs.append(buf)
+            self.flags.append(flg)
+            self._pptrs.append((ctypes.c_void_p * self.world)(*[int(p) for p in hb.buffer_ptrs]))
+            self._fptrs.append((ctypes.c_void_p * self.world)(*[int(p) for p in hf.buffer_ptrs]))
+            self.outs.append(torch.empty((N, M), dtype=torch.float16, device=device))
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)   # every rank's buffers and flags are zero before anybody writes
+        self._turn = 0
+
+    def spmm(self, W_local, B_local, split_k=1, workspace=None, stream=None):
+        """Enqueue this rank's SpMM; its partial [N, M] goes to slot `rank` of every rank's current buffer."""
+        from . import api
+        slot = self._turn % len(self.bufs)
+        api.spmm_allreduce(W_local, B_local, self._pptrs[slot], self._fptrs[slot], self.world, self.rank,
+                           split_k=split_k, workspace=workspace, stream=stream)
+        return slot
+
+    def reduce(self, out=None, stream=None):
+        """Enqueue the wait for all ranks' partials of the current exchange and their sum; returns the [N, M] result."""
+        from . import api
+        slot = self._turn % len(self.bufs)
+        out = self.outs[slot] if out is None else out
+        api.allreduce_finish(out, self.bufs[slot], self.flags[slot], self.world, stream=stream)
+        self._turn += 1
+        return out

@@ -58,6 +58,34 @@ def test_single_rank_exchange_and_chained_wait(lib_built):
     assert sp.device_status() == 0
 
 
+def test_single_rank_allreduce_path(lib_built):
+    """K-split entry points with one rank: the partial goes to slot 0 of the local buffer, the finish kernel waits for
+    the flag and sums one slot, which must reproduce the plain SpMM bit for bit (same kernel, one rounding each)."""
+    import spmspm_b200 as sp
+    sp.reset_device_status()
+    M, K, N = 512, 1024, 16
+    A = make_sparse(M, K, 0.6, seed=61)
+    B = make_dense(N, K, seed=62)
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    Bd = torch.from_numpy(B).cuda()
+    want = sp.spmm(W, Bd, split_k=1)
+    parts = torch.full((1, N, M), 5.0, dtype=torch.float16, device="cuda")
+    flags = torch.zeros(3, dtype=torch.int32, device="cuda")
+    out = torch.zeros((N, M), dtype=torch.float16, device="cuda")
+    pp, fp = (ctypes.c_void_p * 1)(parts.data_ptr()), (ctypes.c_void_p * 1)(flags.data_ptr())
+    for sk in (1, 3):
+        sp.spmm_allreduce(W, Bd, pp, fp, 1, 0, split_k=sk)
+        sp.allreduce_finish(out, parts, flags, 1)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy().astype(np.float32)
+        ref = oracle.gemm_f32(A, B)
+        assert np.abs(got - ref).max() <= 1e-2 * np.abs(ref).max()
+        if sk == 1:
+            assert np.array_equal(out.cpu().numpy().view(np.uint16), want.cpu().numpy().view(np.uint16))
+    assert flags.cpu().tolist() == [2, 2, 2]
+    assert sp.device_status() == 0
+
+
 def test_exchange_argument_checks(lib_built):
     import spmspm_b200 as sp
     A = make_sparse(128, 128, 0.5, seed=1)
@@ -101,6 +129,17 @@ pg.spmm(W, B, lo, split_k=2)                    # a chain: each launch waits for
 pg.spmm(W, B, lo, after=pg)
 pg.spmm(W, B, lo, after=pg, split_k=2)
 bad += check(pg.wait())
+dist.barrier()
+# K-split: every rank multiplies its column slice, the partials are summed over the ranks (one-shot all-reduce)
+klo, khi = spd.col_shard_bounds(K, world, rank)
+Wk = sp.encode_device(torch.from_numpy(np.ascontiguousarray(A[:, klo:khi])).to(dev))
+Bk = B[:, klo:khi].contiguous()
+pr = spd.PeerReduce(N, M, dev)
+for sk in (1, 2, 1):
+    pr.spmm(Wk, Bk, split_k=sk)
+    out = pr.reduce()
+    torch.cuda.synchronize()
+    bad += int(float((out.float() - ref).abs().max()) > 4e-3 * float(ref.abs().max()))
 dist.barrier()
 bad += int(sp.device_status() != 0)
 open(os.path.join(sys.argv[2], f"result_{rank}"), "w").write(str(bad))   # the ranks' prints would interleave
