@@ -253,6 +253,28 @@ int spb_allreduce_finish(void* stream, uint16_t* C, const uint16_t* parts_local,
                          int M_Global, int N_Global);
 
 /*
+ * Linear layer: the SpMM with the element-wise kernels that FasterTransformer runs after each GEMM of the OPT
+ * decoder folded into the place where the result is rounded to fp16 (the SpMM kernel's epilogue, its fused split-K
+ * reduction, or the reduction launch): bias add after QKV and FC1, ReLU after FC1, bias and residual add after the
+ * attention output projection and FC2 (third_party/ft_spinfer.patch:623-862 FFN, 1459-1573 and 1704-1811
+ * attention).  With y = the SpMM result as spb_spmm_bitmap_v3 rounds it:
+ *     y = fp16(y + bias[m])        bias: M_Global fp16 values, or NULL
+ *     y = y <= 0 ? 0 : y           activation 1 (ReLU); 0 = none
+ *     C = fp16(residual + y)       residual: fp16 [N_Global][M_Global] like C, or NULL (may be C itself)
+ * every step rounded to fp16, so the result has the bits of spb_spmm_bitmap_v3 followed by separate element-wise
+ * fp16 kernels.  All other arguments, checks and return values as spb_spmm_bitmap_v3; bias and residual must be
+ * 16-byte aligned.  spb_linear_allreduce_finish is spb_allreduce_finish with the same tail applied to the sum over
+ * the ranks (residual and bias are added once, after the reduction); both run as one kernel launch.
+ */
+int spb_linear_bitmap_v3(void* stream, const uint16_t* Compressed_A, const int* TileOffsets, const int* TileOffsets_Median,
+                         const uint64_t* bitmap, const int* max_nnz_intile, const uint16_t* B, uint16_t* C, int M_Global,
+                         int N_Global, int K_Global, const uint16_t* bias, const uint16_t* residual, int activation,
+                         uint16_t* Reduction_Workspace, int Split_K);
+int spb_linear_allreduce_finish(void* stream, uint16_t* C, const uint16_t* parts_local, uint32_t* flags_local, int n_peers,
+                                int M_Global, int N_Global, const uint16_t* bias, const uint16_t* residual,
+                                int activation);
+
+/*
  * Status word of the current device: 0 when no kernel of this library has hit a
  * bounded wait that ran out or an inconsistent offset since the last reset.
  * Synchronises the device.  spb_reset_device_status clears it.

@@ -44,6 +44,10 @@ SIGNATURES = {
     "spb_spmm_bitmap_v3_allreduce": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,
                                                     ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _vp, ctypes.c_int]),
     "spb_allreduce_finish": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
+    "spb_linear_bitmap_v3": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                            _vp, _vp, ctypes.c_int, _vp, ctypes.c_int]),
+    "spb_linear_allreduce_finish": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _vp,
+                                                   ctypes.c_int]),
     "spb_device_status": (ctypes.c_int, [_i32p]),
     "spb_reset_device_status": (ctypes.c_int, []),
 }

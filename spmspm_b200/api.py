@@ -325,6 +325,49 @@ def spmm(W: BitmapMatrix, B, split_k=None, out=None, workspace=None, stream=None
     return out
 
 
+ACT_NONE, ACT_RELU = 0, 1
+
+
+def _check_tail(M, N, bias, residual, activation, device):
+    if activation not in (ACT_NONE, ACT_RELU):
+        raise SpmmError("activation must be ACT_NONE or ACT_RELU")
+    if bias is not None and not (bias.is_cuda and bias.device == device and bias.dtype == torch.float16
+                                 and bias.is_contiguous() and tuple(bias.shape) == (M,)):
+        raise SpmmError("bias must be a contiguous CUDA float16 [M] tensor")
+    if residual is not None and not (residual.is_cuda and residual.device == device and residual.dtype == torch.float16
+                                     and residual.is_contiguous() and tuple(residual.shape) == (N, M)):
+        raise SpmmError("residual must be a contiguous CUDA float16 [N,M] tensor")
+
+
+def linear(W: BitmapMatrix, B, bias=None, residual=None, activation=ACT_NONE, split_k=None, out=None, workspace=None,
+           stream=None):
+    """spb_linear_bitmap_v3: out[N,M] = residual + act(spmm(W, B) + bias), every step rounded to fp16 (the bits of
+    spmm followed by the separate element-wise fp16 operations), in the launches of the SpMM itself."""
+    if not (B.is_cuda and B.dtype == torch.float16 and B.dim() == 2 and B.is_contiguous() and B.shape[1] == W.K):
+        raise SpmmError("B must be a contiguous CUDA float16 [N,K] tensor")
+    N = B.shape[0]
+    _check_tail(W.M, N, bias, residual, activation, B.device)
+    if split_k is None:
+        split_k = suggest_split_k(W.M, N, W.K)
+    if out is None:
+        out = torch.empty((N, W.M), dtype=torch.float16, device=B.device)
+    elif not (out.is_cuda and out.dtype == torch.float16 and out.is_contiguous() and tuple(out.shape) == (N, W.M)):
+        raise SpmmError("out must be a contiguous CUDA float16 [N,M] tensor")
+    if split_k > 1 and workspace is None:
+        workspace = torch.empty(split_k * N * W.M, dtype=torch.float16, device=B.device)
+    if split_k > 1 and workspace.numel() < split_k * N * W.M:
+        raise SpmmError("workspace too small for split_k * N * M halves")
+    with torch.cuda.device(B.device):
+        _init_if_possible(stream)
+        code = _lib.load().spb_linear_bitmap_v3(_stream_ptr(stream), _ptr(W.vals), _ptr(W.gtile), _ptr(W.mtile),
+                                                _ptr(W.bitmap), _ptr(W.max_nnz), _ptr(B), _ptr(out), W.M, N, W.K,
+                                                _ptr(bias) if bias is not None else None,
+                                                _ptr(residual) if residual is not None else None, int(activation),
+                                                _ptr(workspace) if workspace is not None else None, split_k)
+    _check(code, "spb_linear_bitmap_v3")
+    return out
+
+
 def spmm_noalloc(W: BitmapMatrix, B, split_k, out, stream=None):
     """spb_spmm_bitmap_v3_noalloc: split-K SpMM whose partial sums use the library's built-in scratch array.
 
@@ -380,13 +423,16 @@ def spmm_allreduce(W: BitmapMatrix, B, part_peers, flag_peers, n_peers, rank, B_
     _check(code, "spb_spmm_bitmap_v3_allreduce")
 
 
-def allreduce_finish(out, parts_local, flags_local, n_peers, stream=None):
-    """spb_allreduce_finish: bounded wait for all ranks' partials, then their fp32 sum in rank order, rounded once."""
+def allreduce_finish(out, parts_local, flags_local, n_peers, stream=None, bias=None, residual=None, activation=ACT_NONE):
+    """spb_linear_allreduce_finish: bounded wait for all ranks' partials, then their fp32 sum in rank order, rounded
+    once, then the linear layer's tail (bias, activation, residual; see `linear`).  One launch."""
     N, M = out.shape
+    _check_tail(M, N, bias, residual, activation, out.device)
     with torch.cuda.device(out.device):
-        code = _lib.load().spb_allreduce_finish(_stream_ptr(stream), _ptr(out), _ptr(parts_local), _ptr(flags_local), n_peers,
-                                                M, N)
-    _check(code, "spb_allreduce_finish")
+        code = _lib.load().spb_linear_allreduce_finish(_stream_ptr(stream), _ptr(out), _ptr(parts_local), _ptr(flags_local),
+                                                       n_peers, M, N, _ptr(bias) if bias is not None else None,
+                                                       _ptr(residual) if residual is not None else None, int(activation))
+    _check(code, "spb_linear_allreduce_finish")
     return out
 
 

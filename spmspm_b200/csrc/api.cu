@@ -82,10 +82,18 @@ cudaError_t check_spmm_args(const char* who, const void* vals, const void* gtile
 
 static cudaError_t spmm_checked(cudaStream_t stream, const uint16_t* vals, const int* gtile, const int* mtile,
                                 const uint64_t* bitmap, const int* max_nnz, const uint16_t* B, uint16_t* C, int M,
-                                int N, int K, uint16_t* ws, int split_k)
+                                int N, int K, uint16_t* ws, int split_k, const Epilogue& ep = Epilogue())
 {
     cudaError_t chk = check_spmm_args("SpMM", vals, gtile, mtile, bitmap, max_nnz, B, M, N, K, ws, split_k);
     if (chk != cudaSuccess) return chk;
+    if (ep.activation != 0 && ep.activation != 1) {
+        set_error("SpMM: activation must be 0 (none) or 1 (ReLU), got %d", ep.activation);
+        return cudaErrorInvalidValue;
+    }
+    if (!aligned16(ep.bias) || !aligned16(ep.residual)) {
+        set_error("SpMM: bias and residual must be 16-byte aligned");
+        return cudaErrorMisalignedAddress;
+    }
     if (!C) {
         set_error("SpMM: null device pointer");
         return cudaErrorInvalidValue;
@@ -109,9 +117,10 @@ static cudaError_t spmm_checked(cudaStream_t stream, const uint16_t* vals, const
     bool fused = false;
     a.final_out = C;
     a.reduce_fused = &fused;
+    a.ep = ep;
     cudaError_t e = spmm_launch(stream, a);
     if (e != cudaSuccess || split_k == 1 || fused) return e;
-    return splitk_reduce(stream, C, ws, M, N, split_k);
+    return splitk_reduce(stream, C, ws, M, N, split_k, ep);
 }
 
 struct DevBuf {
@@ -402,6 +411,19 @@ int spb_spmm_bitmap_v3(void* stream, const uint16_t* A, const uint16_t* Compress
     (void)A;
     return (int)spb::spmm_checked((cudaStream_t)stream, Compressed_A, TileOffsets, TileOffsets_Median, bitmap,
                                   max_nnz_intile, B, C, M_Global, N_Global, K_Global, Reduction_Workspace, Split_K);
+}
+
+int spb_linear_bitmap_v3(void* stream, const uint16_t* Compressed_A, const int* TileOffsets, const int* TileOffsets_Median,
+                         const uint64_t* bitmap, const int* max_nnz_intile, const uint16_t* B, uint16_t* C, int M_Global,
+                         int N_Global, int K_Global, const uint16_t* bias, const uint16_t* residual, int activation,
+                         uint16_t* Reduction_Workspace, int Split_K)
+{
+    spb::Epilogue ep;
+    ep.bias = bias;
+    ep.residual = residual;
+    ep.activation = activation;
+    return (int)spb::spmm_checked((cudaStream_t)stream, Compressed_A, TileOffsets, TileOffsets_Median, bitmap,
+                                  max_nnz_intile, B, C, M_Global, N_Global, K_Global, Reduction_Workspace, Split_K, ep);
 }
 
 int spb_splitk_reduce(void* stream, uint16_t* C, const uint16_t* Reduction_Workspace, int M_Global, int N_Global,

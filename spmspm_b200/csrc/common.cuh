@@ -27,7 +27,18 @@ cudaError_t encode_pack(cudaStream_t s, const uint16_t* A, int M, int K, const i
                         uint16_t* vals, size_t vals_capacity, int* status);
 
 // ---- split-K reduction (reduction.cu) --------------------------------------
-cudaError_t splitk_reduce(cudaStream_t s, uint16_t* C, const uint16_t* ws, int M, int N, int split_k);
+// Element-wise tail of a linear layer (see epilogue.cuh): bias [M] fp16 or null, residual in the layout of the
+// destination or null, activation 0 (none) or 1 (ReLU).
+struct Epilogue {
+    const uint16_t* bias = nullptr;
+    const uint16_t* residual = nullptr;
+    int activation = 0;
+    bool any() const { return bias || residual || activation; }
+};
+// ep.residual is indexed like C; wait_flags/wait_n: first wait (bounded) until the n sequence numbers of an
+// exchange have arrived (see exchange.cu), for partials that other GPUs write
+cudaError_t splitk_reduce(cudaStream_t s, uint16_t* C, const uint16_t* ws, int M, int N, int split_k,
+                          const Epilogue& ep = Epilogue(), uint32_t* wait_flags = nullptr, int wait_n = 0, int* status = nullptr);
 
 // ---- SpMM (spmm_kernel.cu) --------------------------------------------------
 struct SpmmArgs {
@@ -54,6 +65,9 @@ struct SpmmArgs {
     // flag array (on this GPU) of the exchange that produced B, or null; wait_n ranks
     uint32_t* wait_flags = nullptr;
     int wait_n = 0;
+    // applied by the kernel wherever it writes final rows; with split_k > 1 and no fused reduction the caller's
+    // reduction launch has to apply it
+    Epilogue ep;
 };
 cudaError_t wait_flags_launch(cudaStream_t s, uint32_t* flags, int n, int* status);
 cudaError_t exchange_counter(cudaStream_t s, int** out);  // a zeroed int of the stream's scratch, for CTA counting

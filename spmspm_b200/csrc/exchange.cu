@@ -221,10 +221,34 @@ extern "C" int spb_spmm_bitmap_v3_allreduce(void* stream, const uint16_t* Compre
 // Second half of the all-reduce: waits (bounded) until every rank's partial of the current exchange has arrived
 // in this rank's buffer, then C = fp16(sum over the ranks, in rank order, of float(partial)), the arithmetic of
 // the split-K reduction.
+extern "C" int spb_linear_allreduce_finish(void* stream, uint16_t* C, const uint16_t* parts_local, uint32_t* flags_local,
+                                           int n_peers, int M_Global, int N_Global, const uint16_t* bias,
+                                           const uint16_t* residual, int activation)
+{
+    if (!flags_local || n_peers < 1 || n_peers > 8) {
+        spb::set_error("spb_allreduce_finish: flags and 1..8 peers required");
+        return (int)cudaErrorInvalidValue;
+    }
+    if (!C || !parts_local || M_Global <= 0 || N_Global <= 0 || (M_Global % 64) || !spb::aligned16(C) ||
+        !spb::aligned16(parts_local) || !spb::aligned16(bias) || !spb::aligned16(residual) ||
+        (activation != 0 && activation != 1)) {
+        spb::set_error("spb_allreduce_finish: bad argument");
+        return (int)cudaErrorInvalidValue;
+    }
+    int* status = nullptr;
+    cudaError_t e = spb::device_status_ptr(&status);
+    if (e != cudaSuccess) return (int)e;
+    spb::Epilogue ep;
+    ep.bias = bias;
+    ep.residual = residual;
+    ep.activation = activation;
+    // one launch: every block first polls the flags, then sums its part of the slots
+    return (int)spb::splitk_reduce((cudaStream_t)stream, C, parts_local, M_Global, N_Global, n_peers, ep, flags_local,
+                                   n_peers, status);
+}
+
 extern "C" int spb_allreduce_finish(void* stream, uint16_t* C, const uint16_t* parts_local, uint32_t* flags_local,
                                     int n_peers, int M_Global, int N_Global)
 {
-    int rc = spb_wait_flags(stream, flags_local, n_peers);
-    if (rc != 0) return rc;
-    return spb_splitk_reduce(stream, C, parts_local, M_Global, N_Global, n_peers);
+    return spb_linear_allreduce_finish(stream, C, parts_local, flags_local, n_peers, M_Global, N_Global, nullptr, nullptr, 0);
 }

@@ -31,6 +31,7 @@
 // bounded: when one runs out the CTA records it in the device status word and leaves without
 // touching tensor memory again.
 #include "common.cuh"
+#include "epilogue.cuh"
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cstdio>
@@ -127,6 +128,12 @@ struct KernelParams {
     int* counters;
     int balanced, units;
     int weights_ahead;  // 1: the weight-streaming warps do not wait for the stream's preceding kernel
+    // element-wise tail of a linear layer (exchange variants only), applied where final rows are written:
+    // bias by weight row, residual at the position of the row in the first destination buffer
+    const uint16_t* ep_bias;
+    const uint16_t* ep_res;
+    int ep_act;
+    int ep_on;
     // Output: normally one buffer [N][M] (or the split-K partials).  For the fused all-gather the rows of this
     // launch go to rows row0.. of n_out buffers [N][ld_out], this GPU's and its peers' (peer memory mapped
     // into this process), and when the last CTA has finished, the launch's sequence number is written to
@@ -1026,6 +1033,8 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
 #pragma unroll
                 for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
                 const size_t at = (size_t)col * p.red_ld + (size_t)p.red_row0 + rowg;
+                if (kExchange && p.ep_on)
+                    o = ep_apply8(o, p.ep_bias ? p.ep_bias + rowg : nullptr, p.ep_res ? p.ep_res + at : nullptr, p.ep_act);
                 for (int q = 0; q < p.n_red; ++q) *reinterpret_cast<uint4*>(p.red_outs[q] + at) = o;
             }
         };
@@ -1129,6 +1138,17 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
 #pragma unroll
                 for (int n = 0; n < 16; ++n) h[n] = __half_as_ushort(__float2half_rn(acc[n]));
                 const int col0 = w.nt * NPAD + c * 16;
+                if (kExchange && p.ep_on && p.split_k == 1 && grow < p.M) {   // these are final rows
+                    const bool hb = p.ep_bias != nullptr, hr = p.ep_res != nullptr;
+                    const __half b = hb ? __ushort_as_half(p.ep_bias[grow]) : __ushort_as_half((unsigned short)0);
+                    uint16_t r[16];
+#pragma unroll
+                    for (int n = 0; n < 16; ++n)
+                        r[n] = hr && col0 + n < p.N ? p.ep_res[out0 + (size_t)(col0 + n) * p.ld_out] : (uint16_t)0;
+#pragma unroll
+                    for (int n = 0; n < 16; ++n)
+                        h[n] = __half_as_ushort(ep_one(__ushort_as_half(h[n]), hb, b, p.ep_act, hr, __ushort_as_half(r[n])));
+                }
                 if (grow < p.M) {
 #pragma unroll 1
                     for (int q = 0; q < n_out; ++q) {
@@ -1632,6 +1652,10 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     p.wait_flags = a.wait_flags;
     p.wait_n = a.wait_n;
     p.weights_ahead = g_weights_ahead.load();
+    p.ep_bias = a.ep.bias;
+    p.ep_res = a.ep.residual;
+    p.ep_act = a.ep.activation;
+    p.ep_on = a.ep.any() ? 1 : 0;
     const int mode = g_schedule.load();
     if (mode != 1 && t_static_depth == 0 && (units + 1) * di.sms < (1LL << 31) && p.num_items <= kCounterCap &&
         no_empty_range && (mode == 2 || prefer_balanced(p.row_blocks, p.n_tiles, p.kt_total, a.split_k, di.sms, NPAD))) {
@@ -1672,7 +1696,7 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
         p.done = sc->counters + kCounterCap;
     }
 
-    const bool exchange = gather || p.wait_flags != nullptr;
+    const bool exchange = gather || p.wait_flags != nullptr || p.ep_on;
     const int variant = (exchange ? 2 : 0) + (p.balanced ? 1 : 0);
     auto kernel = variant == 3   ? spmm_bitmap_tcgen05_kernel<NPAD, true, true>
                   : variant == 2 ? spmm_bitmap_tcgen05_kernel<NPAD, true, false>

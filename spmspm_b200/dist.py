@@ -166,11 +166,13 @@ class PeerReduce:
                            split_k=split_k, workspace=workspace, stream=stream)
         return slot
 
-    def reduce(self, out=None, stream=None):
-        """Enqueue the wait for all ranks' partials of the current exchange and their sum; returns the [N, M] result."""
+    def reduce(self, out=None, stream=None, bias=None, residual=None, activation=0):
+        """Enqueue the wait for all ranks' partials of the current exchange and their sum (then the linear layer's
+        tail: bias, activation, residual, see spmspm_b200.linear); returns the [N, M] result."""
         from . import api
         slot = self._turn % len(self.bufs)
         out = self.outs[slot] if out is None else out
-        api.allreduce_finish(out, self.bufs[slot], self.flags[slot], self.world, stream=stream)
+        api.allreduce_finish(out, self.bufs[slot], self.flags[slot], self.world, stream=stream, bias=bias,
+                             residual=residual, activation=activation)
         self._turn += 1
         return out

@@ -47,7 +47,8 @@ class SparseOptDecoderLayer:
     """
 
     def __init__(self, hidden, heads, ffn, sparsity, device, batch, max_len, group=None, reduce="peer", seed=0x5EED0005,
-                 keep_dense=False):
+                 keep_dense=False, fused=True):
+        self.fused = fused   # bias / ReLU / residual inside the SpMM's launches (spb_linear_bitmap_v3) or as torch ops
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -96,24 +97,41 @@ class SparseOptDecoderLayer:
             self.split[key] = sk
         return self.split[key]
 
-    def _linear(self, name, x):
-        """x [N, K_local] -> [N, M_local] (no bias)."""
-        return api.spmm(self.W[name], x, split_k=self._split_k(name, x.shape[0]), workspace=self.ws)
+    def _linear(self, name, x, bias=None, residual=None, relu=False):
+        """x [N, K_local] -> residual + act(x W^T + bias) [N, M_local]; with `fused` in the SpMM's own launches."""
+        sk = self._split_k(name, x.shape[0])
+        if self.fused:
+            return api.linear(self.W[name], x, bias=bias, residual=residual, activation=api.ACT_RELU if relu else api.ACT_NONE,
+                              split_k=sk, workspace=self.ws)
+        return self._tail(api.spmm(self.W[name], x, split_k=sk, workspace=self.ws), bias, residual, relu)
 
-    def _linear_reduced(self, name, x):
-        """K-split linear layer: x [N, K/P] -> all-reduced [N, M]."""
+    @staticmethod
+    def _tail(y, bias, residual, relu):
+        if bias is not None:
+            y = y + bias
+        if relu:
+            y = torch.relu(y)
+        if residual is not None:
+            y = residual + y
+        return y
+
+    def _linear_reduced(self, name, x, bias, residual):
+        """K-split linear layer: x [N, K/P] -> residual + (all-reduced x W^T + bias) [N, M]."""
         N = x.shape[0]
+        if self.reduce_kind == "none":
+            return self._linear(name, x, bias, residual)
         if self.reduce_kind == "peer":
             key = (name, N)
             if key not in self._peer:
                 self._peer[key] = spd.PeerReduce(N, self.W[name].M, self.device, self.group, slots=1)
             pr = self._peer[key]
             pr.spmm(self.W[name], x, split_k=self._split_k(name, N), workspace=self.ws)
-            return pr.reduce()
+            if self.fused:
+                return pr.reduce(bias=bias, residual=residual)
+            return self._tail(pr.reduce(), bias, residual, False)
         y = self._linear(name, x)
-        if self.reduce_kind == "nccl":
-            dist.all_reduce(y, group=self.group)
-        return y
+        dist.all_reduce(y, group=self.group)
+        return self._tail(y, bias, residual, False)
 
     def prepare(self, Ns):
         """Create the exchange buffers for the activation widths that will be used (symmetric-memory allocation is a
@@ -136,7 +154,7 @@ class SparseOptDecoderLayer:
         cache position.  Returns [batch * T, h]."""
         Bn, hp, d = self.batch, self.hp, self.d
         h1 = F.layer_norm(x, (self.h,), self.ln1_w, self.ln1_b)
-        qkv = self._linear("qkv", h1) + self.b_qkv                                   # [N, 3h/P]
+        qkv = self._linear("qkv", h1, self.b_qkv)                                    # [N, 3h/P]
         q, k, v = (t.reshape(Bn, T, self.heads_p, d).transpose(1, 2) for t in qkv.split(hp, dim=1))   # [B, H/P, T, d]
         idx = self.pos + self.arange[:T]                                             # device-side positions
         self.k_cache.index_copy_(2, idx, k.contiguous())
@@ -145,10 +163,10 @@ class SparseOptDecoderLayer:
         mask = self.arange[None, :] <= (self.pos + self.arange[:T])[:, None]         # [T, max_len]
         attn = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask[None, None])
         attn = attn.transpose(1, 2).reshape(Bn * T, hp).contiguous()
-        x = x + self._linear_reduced("out", attn) + self.b_out
+        x = self._linear_reduced("out", attn, self.b_out, x)
         h2 = F.layer_norm(x, (self.h,), self.ln2_w, self.ln2_b)
-        f1 = torch.relu(self._linear("fc1", h2) + self.b_fc1)
-        x = x + self._linear_reduced("fc2", f1) + self.b_fc2
+        f1 = self._linear("fc1", h2, self.b_fc1, relu=True)
+        x = self._linear_reduced("fc2", f1, self.b_fc2, x)
         self.pos += T
         return x
 

@@ -124,3 +124,14 @@ def test_spmm_entry_points_reject_bad_arguments_without_launching(lib_built):
     for name in ("vals", "mt", "bm", "B"):
         assert gather(**{name: ok + 4}) == MISALIGNED, name
     assert gather(sk=2, ws=ok + 2) == MISALIGNED
+
+    def linear(act=0, bias=ok, res=ok, **over):
+        a = dict(args, **over)
+        return lib.spb_linear_bitmap_v3(None, a["vals"], a["gt"], a["mt"], a["bm"], a["mx"], a["B"], a["C"], 128, 16, 128,
+                                        bias, res, act, a["ws"], 1)
+
+    assert linear(act=2) == INVALID and linear(act=-1) == INVALID and linear(vals=None) == INVALID
+    assert linear(bias=ok + 2) == MISALIGNED and linear(res=ok + 8) == MISALIGNED
+    assert lib.spb_linear_allreduce_finish(None, ok, ok, ok, 1, 128, 16, ok + 2, None, 0) == INVALID
+    assert lib.spb_linear_allreduce_finish(None, ok, ok, ok, 1, 128, 16, None, None, 3) == INVALID
+    assert lib.spb_linear_allreduce_finish(None, ok, ok, None, 1, 128, 16, None, None, 0) == INVALID
