@@ -65,8 +65,10 @@ namespace {
 //   warpgroup 2..: decode groups (one warp per quadrant each)
 // A pipeline stage holds kKT consecutive k-tiles of one 128-row block, one for each of the four decode
 // groups.  (Stages of one or two k-tiles mean more stages in the shared-memory ring and more copies per
-// byte; they measured 1.7x and 1.15x slower.)
+// byte; they measured 1.7x and 1.15x slower.)  Activation tiles wider than 64 columns leave room for two k-tiles
+// per stage only (stage_kt).
 constexpr int kKT = 4;
+__host__ __device__ constexpr int stage_kt(int npad) { return npad > 64 ? 2 : 4; }
 #ifndef SPB_GROUPS
 #define SPB_GROUPS 4
 #endif
@@ -77,7 +79,10 @@ static_assert(kDecodeGroups >= kKT && kDecodeGroups <= 6, "a stage must not give
 // A operand blocks in tensor memory (32 columns = one k-tile each), used in turn: k-tile t uses block t % kABlocks.
 // With the accumulators kept to 128 columns there is room for 12: a group that expands kUnit k-tiles per turn can
 // start its next turn while the tensor core still reads the blocks of its last one.
+// Activation tiles of 256 columns need 256 columns of tensor memory for their accumulator, tiles of 128 columns
+// get two accumulators (the epilogue of a work item then overlaps the MMAs of the next): 8 blocks are left.
 constexpr int kABlocks = 12;
+__host__ __device__ constexpr int a_blocks(int npad) { return npad >= 128 ? 8 : 12; }
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
@@ -326,10 +331,11 @@ __device__ __forceinline__ bool bar_and_epilogue(bool pred)
     return r != 0;
 }
 // Bits of the nv A operand blocks that follow block tb in the ring of kABlocks.
+template <int kBlocks>
 __device__ __forceinline__ uint32_t block_mask(uint32_t tb, int nv)
 {
     const uint32_t m = ((1u << nv) - 1u) << tb;
-    return (m | (m >> kABlocks)) & ((1u << kABlocks) - 1u);
+    return (m | (m >> kBlocks)) & ((1u << kBlocks) - 1u);
 }
 // A work item is a run of k-tiles of one 128-row block (and one activation tile column): a whole split-K
 // range, or, with the balanced schedule, a piece of one.
@@ -597,6 +603,10 @@ template <int NPAD, bool kExchange, bool kBalanced>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtensorMap tmap_b)
 {
+    // this width's k-tiles per stage and A operand blocks (they hide the file-scope defaults of the same names)
+    constexpr int kKT = stage_kt(NPAD);
+    constexpr int kABlocks = a_blocks(NPAD);
+    static_assert(kDecodeGroups >= kKT, "a stage must not give a group two k-tiles");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled activation tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -623,8 +633,8 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     // Back-to-back tcgen05.mma into one accumulator are serialised by the tensor core, and at these
     // tiny N every instruction is pure latency, so the four k-steps of a k-tile go to different
     // accumulators (summed in the epilogue).
-    constexpr int kNAcc = NPAD <= 16 ? 4 : 2;
-    constexpr int kAccBufs = NPAD <= 32 ? 2 : 1;
+    constexpr int kNAcc = NPAD <= 16 ? 4 : NPAD <= 64 ? 2 : 1;
+    constexpr int kAccBufs = NPAD <= 32 || NPAD == 128 ? 2 : 1;
     constexpr uint32_t kAccCols = kAccBufs * kNAcc * NPAD;
     constexpr uint32_t kACols = kABlocks * 32;
     static_assert(kAccCols + kACols <= 512, "TMEM budget");
@@ -952,7 +962,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         if (pacc[6] == 0 && lane == 0) { PROF_EV(5); pacc[6] = 1; }
 #endif
                     }
-                    ph ^= block_mask(tb, nv);
+                    ph ^= block_mask<kABlocks>(tb, nv);
                     tb = (tb + (uint32_t)nv) % kABlocks;
                     if (++slot == (uint32_t)S) {
                         slot = 0;
@@ -1072,6 +1082,16 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 // straight from its registers, without publishing its own sums first.
                 if (leader) arrived = ld_acquire_gpu(p.counters + w.id);
             }
+            // Tail of a linear layer (exchange variants): the row's bias is fetched now, the residual values of a
+            // 16-column chunk before the chunk's accumulators are read, so that no global-memory latency sits
+            // between the reads of tensor memory (the accumulators are released after the last of them).
+            const bool tail = kExchange && p.ep_on && p.split_k == 1 && grow < p.M;
+            const bool tail_bias = tail && p.ep_bias != nullptr, tail_res = tail && p.ep_res != nullptr;
+            const uint16_t ep_b = tail_bias ? p.ep_bias[grow] : (uint16_t)0;
+            const int tail_act = p.ep_act;
+            uint16_t ep_r[16];
+#pragma unroll
+            for (int n = 0; n < 16; ++n) ep_r[n] = 0;
             const uint32_t accbuf = idx % kAccBufs;
             ok = mbar_wait_relaxed(bar_accfull + 8 * accbuf, (idx / kAccBufs) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
@@ -1138,16 +1158,15 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
 #pragma unroll
                 for (int n = 0; n < 16; ++n) h[n] = __half_as_ushort(__float2half_rn(acc[n]));
                 const int col0 = w.nt * NPAD + c * 16;
-                if (kExchange && p.ep_on && p.split_k == 1 && grow < p.M) {   // these are final rows
-                    const bool hb = p.ep_bias != nullptr, hr = p.ep_res != nullptr;
-                    const __half b = hb ? __ushort_as_half(p.ep_bias[grow]) : __ushort_as_half((unsigned short)0);
-                    uint16_t r[16];
+                if (kExchange && tail) {   // these are final rows: two columns per step
+                    const __half2 b2 = __half2half2(__ushort_as_half(ep_b));
 #pragma unroll
-                    for (int n = 0; n < 16; ++n)
-                        r[n] = hr && col0 + n < p.N ? p.ep_res[out0 + (size_t)(col0 + n) * p.ld_out] : (uint16_t)0;
-#pragma unroll
-                    for (int n = 0; n < 16; ++n)
-                        h[n] = __half_as_ushort(ep_one(__ushort_as_half(h[n]), hb, b, p.ep_act, hr, __ushort_as_half(r[n])));
+                    for (int n = 0; n < 16; n += 2) {
+                        const __half2 y = ep_pair(__halves2half2(__ushort_as_half(h[n]), __ushort_as_half(h[n + 1])), tail_bias, b2, tail_act,
+                                                  tail_res, __halves2half2(__ushort_as_half(ep_r[n]), __ushort_as_half(ep_r[n + 1])));
+                        h[n] = __half_as_ushort(__low2half(y));
+                        h[n + 1] = __half_as_ushort(__high2half(y));
+                    }
                 }
                 if (grow < p.M) {
 #pragma unroll 1
@@ -1159,8 +1178,14 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     }
                 }
             };
-#pragma unroll
+#pragma unroll(kExchange && NPAD >= 128 ? 1 : 16)
             for (int c = 0; c < NPAD / 16; ++c) {
+                if (kExchange && tail_res) {
+                    const int col0 = w.nt * NPAD + c * 16;
+#pragma unroll
+                    for (int n = 0; n < 16; ++n)
+                        ep_r[n] = col0 + n < p.N ? p.ep_res[out0 + (size_t)(col0 + n) * p.ld_out] : (uint16_t)0;
+                }
                 uint32_t r[16];
                 tc_ld_32x32b_x16(t_acc + 16 * c, r);
 #pragma unroll
@@ -1213,6 +1238,12 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         float acc[16];
 #pragma unroll
                         for (int n = 0; n < 16; ++n) acc[n] = 0.f;
+                        if (kExchange && tail_res) {
+                            const int col0 = w.nt * NPAD + c * 16;
+#pragma unroll
+                            for (int n = 0; n < 16; ++n)
+                                ep_r[n] = col0 + n < p.N ? p.ep_res[out0 + (size_t)(col0 + n) * p.ld_out] : (uint16_t)0;
+                        }
                         add_all_pairs(acc, c);
                         write_out(acc, c);
                     }
@@ -1374,7 +1405,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
-                const uint32_t mask = block_mask(tb, nv);
+                const uint32_t mask = block_mask<kABlocks>(tb, nv);
                 used |= mask;
                 ph ^= mask;
                 tb = (tb + (uint32_t)nv) % kABlocks;
@@ -1487,7 +1518,7 @@ const ScratchSet* scratch_for(cudaStream_t st, int dev, int sms, bool may_create
     for (int i = 0; i < kScratchSets; ++i) {
         if (sets[i].taken) continue;
         ScratchSet n;
-        const size_t pbytes = (size_t)2 * sms * 128 * 64 * sizeof(float);
+        const size_t pbytes = (size_t)2 * sms * 128 * 256 * sizeof(float);  // two slots of 128 x (widest tile) per CTA
         if (cudaMalloc(&n.partials, pbytes) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;
@@ -1522,13 +1553,23 @@ bool stream_is_capturing(cudaStream_t st)
 // fitted to timings of OPT-shaped matrices at N = 16 and 32.  Every work item after an SM's first costs
 // about 4 k-tiles (pipeline hand-over), a split-K reduction launch about 3.  The exchange of partial sums at
 // the end of a balanced kernel costs about 6 plus 2.2 per round of loads: one round per 16 columns and per
-// other SM that shares a range.
-double static_cost(int row_blocks, int n_tiles, int kt, int sk, int sms)
+// other SM that shares a range.  With activation tiles of 128 and 256 columns a k-tile takes 1.15 and 1.85 units
+// (the tensor core's and the decode warps' shared-memory traffic add up), and the fp16 partials of a split-K run
+// (written once, read once, at about 4 TB/s out of L2 and HBM) stop being negligible.
+double tile_units(int npad) { return npad <= 64 ? 1.0 : npad <= 128 ? 1.15 : 1.85; }
+double item_units(int npad) { return npad <= 64 ? 4.0 : 4.0 + npad / 16; }   // hand-over between work items: the epilogue grows with the tile
+double reduction_cost(int row_blocks, int n_tiles, int sk, int npad)
+{
+    if (sk <= 1) return 0.0;
+    const double bytes = 2.0 * (sk + 1) * (128.0 * row_blocks) * ((double)n_tiles * npad);
+    return 3.0 + 0.15 * sk + bytes / 4.0e6 / 0.45;
+}
+double static_cost(int row_blocks, int n_tiles, int kt, int sk, int sms, int npad)
 {
     const int avg = (kt - 1) / sk + 1;
     const long items = (long)row_blocks * n_tiles * sk;
     const long waves = (items + sms - 1) / sms;
-    return (double)waves * (avg + 4.0) - 4.0 + (sk > 1 ? 3.0 + 0.15 * sk : 0.0);
+    return (double)waves * (tile_units(npad) * avg + item_units(npad)) - item_units(npad) + reduction_cost(row_blocks, n_tiles, sk, npad);
 }
 double balanced_cost(int row_blocks, int n_tiles, int kt, int sk, int sms, int npad)
 {
@@ -1544,11 +1585,11 @@ double balanced_cost(int row_blocks, int n_tiles, int kt, int sk, int sms, int n
         exchange = 6.0 + 2.2 * (npad / 16) * others;
     }
     // the balanced variant of the kernel needs about 4 % longer per k-tile than the static one
-    return 1.04 * share + exchange + (sk > 1 ? 3.0 + 0.15 * sk : 0.0);
+    return 1.04 * tile_units(npad) * share + exchange + reduction_cost(row_blocks, n_tiles, sk, npad);
 }
 bool prefer_balanced(int row_blocks, int n_tiles, int kt, int sk, int sms, int npad)
 {
-    return balanced_cost(row_blocks, n_tiles, kt, sk, sms, npad) < static_cost(row_blocks, n_tiles, kt, sk, sms);
+    return balanced_cost(row_blocks, n_tiles, kt, sk, sms, npad) < static_cost(row_blocks, n_tiles, kt, sk, sms, npad);
 }
 
 template <int NPAD>
@@ -1572,6 +1613,8 @@ cudaError_t prepare_kernels(int dev, int dyn_smem)
     cudaError_t e = prepare_width<16>(dyn_smem);
     if (e == cudaSuccess) e = prepare_width<32>(dyn_smem);
     if (e == cudaSuccess) e = prepare_width<64>(dyn_smem);
+    if (e == cudaSuccess) e = prepare_width<128>(dyn_smem);
+    if (e == cudaSuccess) e = prepare_width<256>(dyn_smem);
     if (e == cudaSuccess) done[dev] = true;
     return e;
 }
@@ -1812,21 +1855,22 @@ int suggest_split_k(int M, int N, int K)
     const int sms = di.ok ? di.sms : 148;
     const int row_blocks = (M / 64 + 1) / 2;
     const int kt = K / 64;
-    const int n_tiles = N <= 64 ? 1 : (N + 63) / 64;
+    const int npad = N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256;   // as spmm_launch picks it
+    const int n_tiles = (N + npad - 1) / npad;
     if (row_blocks <= 0 || kt <= 0) return 1;
     const bool may_balance = g_schedule.load() != 1 && t_static_depth == 0;
     int best = 1;
-    double best_cost = static_cost(row_blocks, n_tiles, kt, 1, sms);
+    double best_cost = static_cost(row_blocks, n_tiles, kt, 1, sms, npad);
     if (may_balance) {
         // Split_K = 1 with equal shares needs no fp16 partial sums and no reduction
-        const double c = balanced_cost(row_blocks, n_tiles, kt, 1, sms, N <= 16 ? 16 : N <= 32 ? 32 : 64);
+        const double c = balanced_cost(row_blocks, n_tiles, kt, 1, sms, npad);
         if (c < best_cost) best_cost = c;
     }
     for (int sk = 2; sk <= 32 && sk <= kt; ++sk) {
         const int avg = (kt - 1) / sk + 1;
         if ((sk - 1) * avg >= kt) continue;  // would leave an empty last range
         if (avg < 4) break;
-        const double cost = static_cost(row_blocks, n_tiles, kt, sk, sms);
+        const double cost = static_cost(row_blocks, n_tiles, kt, sk, sms, npad);
         if (cost < best_cost - 1e-9) {
             best_cost = cost;
             best = sk;
@@ -1845,11 +1889,14 @@ cudaError_t spmm_launch(cudaStream_t s, const SpmmArgs& a)
     int* status = nullptr;
     cudaError_t e = device_status_ptr(&status);
     if (e != cudaSuccess) return e;
-    // Activation tile width: the smallest of 16/32/64 that holds N; wider N is cut into tiles of 64
-    // columns (each re-reads and re-expands the weight).
+    // Activation tile width: the smallest of 16/32/64/128/256 that holds N; wider N (the prefill regime) is cut
+    // into tiles of 256 columns, each of which re-reads and re-expands the weight: at 256 columns the tensor
+    // core's time per k-tile (4 MMAs of 128 x 256 x 16) is about what the expansion of the k-tile takes.
     if (a.N <= 16) return launch_t<16>(s, a, di, status);
     if (a.N <= 32) return launch_t<32>(s, a, di, status);
-    return launch_t<64>(s, a, di, status);
+    if (a.N <= 64) return launch_t<64>(s, a, di, status);
+    if (a.N <= 128) return launch_t<128>(s, a, di, status);
+    return launch_t<256>(s, a, di, status);
 }
 
 }  // namespace spb

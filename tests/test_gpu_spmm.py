@@ -47,7 +47,12 @@ def _run(sp, A, B, split_k):
     (256, 512, 32, 0.6, 3),      # split-K not dividing the 8 k-tiles
     (1024, 1024, 64, 0.4, 4),
     (512, 1024, 128, 0.5, 1),
-    (512, 1024, 256, 0.5, 2),    # two activation tiles
+    (512, 1024, 256, 0.5, 2),    # one 256-column activation tile (stages of two k-tiles, 8 operand blocks)
+    (256, 1024, 100, 0.6, 1),    # 128-column tile, partly filled
+    (384, 2048, 129, 0.6, 3),    # 256-column tile, barely more than 128
+    (512, 1024, 512, 0.6, 1),    # two 256-column tiles (prefill: batch x sequence)
+    (256, 512, 600, 0.5, 2),     # three tiles, the last partly filled
+    (128, 4096, 256, 0.0, 1),    # dense tiles with the widest activation tile: a single stage fits
     (512, 1024, 24, 0.7, 1),     # N the reference rejects
     (256, 2048, 1, 0.6, 1),
     (128, 4096, 16, 0.0, 1),     # fully dense tiles (4096 values per global tile)
@@ -79,7 +84,9 @@ def test_spmm_matches_fp32_oracle(sp, M, K, N, s, sk):
     (5120, 5120, 16, 0.6, 1),     # 3200 k-tiles over the SMs: every range is cut between several SMs
     (4096, 4096, 32, 0.5, 6),     # ranges of 11 k-tiles, shares of 13.8
     (192, 64 * 40, 16, 0.5, 1),   # fewer k-tiles than SMs, half-filled last row block
-    (1024, 1024, 128, 0.5, 3),    # two activation tiles
+    (1024, 1024, 128, 0.5, 3),    # 128-column tile
+    (2048, 2048, 512, 0.6, 1),    # two 256-column tiles, ranges shared between SMs
+    (1024, 4096, 320, 0.6, 2),
     (15360, 5120, 8, 0.6, 1),     # OPT-13B QKV
 ])
 def test_balanced_schedule_repeatable_and_close_to_static(sp, M, K, N, s, sk):
