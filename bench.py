@@ -307,7 +307,7 @@ def main():
     gathered = {(i, N): torch.empty((world, N, mats[i].M), dtype=torch.float16, device=dev) for (i, N) in acts} \
         if world > 1 else None
     order = [(i, N) for N in NS for i in range(len(SHAPES))]
-    launches_per_step = sum(1 + (1 if splits[k] > 1 else 0) for k in order)
+    launches_per_step = None   # counted by the library while a step is issued (spb_launch_count)
     alg_bytes_step = sum(mats[i].algorithmic_bytes(N) for (i, N) in order)
 
     # Several GPUs, peer exchange: one symmetric output buffer per SpMM of the step; every SpMM waits (inside its
@@ -385,7 +385,9 @@ def main():
     # eager figure is reported beside it.
     with torch.cuda.stream(work):
         for w_ in range(args.warmup):
+            n0 = sp.launch_count()
             step(w_ % copies)
+            launches_per_step = sp.launch_count() - n0   # the library's own kernels only (no NCCL, no torch)
     work.synchronize()
     with torch.cuda.stream(work):
         eager_ms = timed(lambda i: step(i % copies), args.steps) / args.steps
@@ -487,7 +489,8 @@ def main():
                    "split_k": {f"{SHAPES[i][0]}x{SHAPES[i][1]}xN{N}": splits[(i, N)] for (i, N) in order},
                    "schedule": args.schedule,
                    "parallelism": f"tp{world}_m_split_allgather_{exchange}" if world > 1 else "single_gpu",
-                   "l2": l2_note, "weight_copies": copies},
+                   "l2": l2_note, "weight_copies": copies, "algorithmic_bytes_per_step": alg_bytes_step,
+                   "launches_per_step": launches_per_step},
         "hbm_gbs": achieved * world if world > 1 else achieved,
         "e2e": {"value": flops_per_step() / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
@@ -545,6 +548,7 @@ def run_layer(args, sp, dist, dev, rank, world, local_rank):
             total, pre, per_step, graphed = generate_timed(layer, prompt, new, steps=max(args.steps // 4, 2), warmup=2)
         results[kind] = {"s_per_generation": total, "prefill_ms": pre * 1e3, "decode_step_us": per_step * 1e6,
                          "decode_graph": graphed, "tokens_per_s": batch * new / total, "clocks": clocks.summary(),
+                         "library_launches": {"prefill": layer.launches[0], "decode_step": layer.launches[1]},
                          "device_status": sp.device_status()}
         del layer
         torch.cuda.empty_cache()
@@ -559,6 +563,7 @@ def run_layer(args, sp, dist, dev, rank, world, local_rank):
                            "parallelism": f"tp{world}_ft_split_allreduce_{best}" if world > 1 else "single_gpu"},
                 "tokens_per_s_per_gpu": r["tokens_per_s"] / world,
                 "tokens_per_s_64_layers": r["tokens_per_s"] / 64.0,
+                "gpu_launches": (r["library_launches"]["prefill"] + new * r["library_launches"]["decode_step"]) * max(args.steps // 4, 2),
                 "by_reduce": results, "clocks": r["clocks"], "device_status": r["device_status"]}
         print(json.dumps(line), flush=True)
     if world > 1:

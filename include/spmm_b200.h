@@ -186,6 +186,9 @@ int spb_splitk_reduce(void* stream, uint16_t* C, const uint16_t* Reduction_Works
  */
 int spb_suggest_split_k(int M, int N, int K);
 
+/* Number of kernel launches this library has issued in this process so far (all entry points, all threads). */
+unsigned long long spb_launch_count(void);
+
 /*
  * Work schedule of spb_spmm_bitmap_v3 (no counterpart in the reference, whose grid is one CTA per
  * output tile and split-K range, csrc/SpMM_API.cuh:61-67).

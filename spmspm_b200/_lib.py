@@ -48,6 +48,7 @@ SIGNATURES = {
                                             _vp, _vp, ctypes.c_int, _vp, ctypes.c_int]),
     "spb_linear_allreduce_finish": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _vp,
                                                    ctypes.c_int]),
+    "spb_launch_count": (ctypes.c_ulonglong, []),
     "spb_device_status": (ctypes.c_int, [_i32p]),
     "spb_reset_device_status": (ctypes.c_int, []),
 }

@@ -448,6 +448,11 @@ def splitk_reduce(C, workspace, M, N, split_k, stream=None):
            "spb_splitk_reduce")
 
 
+def launch_count():
+    """spb_launch_count: kernel launches issued by the library in this process so far."""
+    return int(_lib.load().spb_launch_count())
+
+
 def device_status():
     st = ctypes.c_int(0)
     _check(_lib.load().spb_device_status(ctypes.byref(st)), "spb_device_status")

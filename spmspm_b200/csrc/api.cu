@@ -5,6 +5,7 @@
 #include "common.cuh"
 
 #include <cstdarg>
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -45,6 +46,9 @@ cudaError_t device_status_ptr(int** out)
     *out = cache[dev];
     return cudaSuccess;
 }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 bool aligned16(const void* p)
 {
@@ -438,6 +442,8 @@ int spb_splitk_reduce(void* stream, uint16_t* C, const uint16_t* Reduction_Works
 }
 
 int spb_suggest_split_k(int M, int N, int K) { return spb::suggest_split_k(M, N, K); }
+
+unsigned long long spb_launch_count(void) { return spb::g_launches.load(); }
 
 int spb_init(void* stream) { return (int)spb::init_stream((cudaStream_t)stream); }
 

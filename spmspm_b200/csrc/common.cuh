@@ -84,6 +84,9 @@ void pop_static_schedule();
 cudaError_t reset_schedule_scratch();  // clears the arrival counters of the current device
 
 void set_error(const char* fmt, ...);
+// Kernel launches this library has issued in this process (every launch site counts itself): lets a caller state
+// how many kernels a piece of work takes, e.g. by reading the counter around the capture of a CUDA graph.
+void count_launch(int n = 1);
 bool aligned16(const void* p);
 // Argument checks of the SpMM entry points (api.cu): cudaSuccess, or an error code with the message set.
 cudaError_t check_spmm_args(const char* who, const void* vals, const void* gtile, const void* mtile, const void* bitmap,

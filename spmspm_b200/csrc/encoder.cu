@@ -208,6 +208,7 @@ cudaError_t encode_count_and_scan(cudaStream_t s, const uint16_t* A, int M, int 
                                   int* gtile, uint64_t* bitmap, int* max_nnz, void* scratch)
 {
     const int GK = K / 64, G = (M / 64) * GK;
+    count_launch(G > 0 ? 3 : 2);
     encode_init_kernel<<<1, 1, 0, s>>>(max_nnz);
     if (G > 0) {
         encode_count_kernel<<<G, kEncThreads, 0, s>>>(A, K, GK, tile_nnz, mtile, (int*)scratch, bitmap, max_nnz);
@@ -221,6 +222,7 @@ cudaError_t encode_pack(cudaStream_t s, const uint16_t* A, int M, int K, const i
 {
     (void)bitmap;
     const int GK = K / 64, G = (M / 64) * GK;
+    if (G > 0) count_launch();
     if (G > 0) encode_pack_kernel<<<G, kEncThreads, 0, s>>>(A, K, GK, gtile, vals, vals_capacity, status);
     return cudaGetLastError();
 }

@@ -92,6 +92,7 @@ splitk_reduce_gather_kernel(const GatherOut g, const uint16_t* __restrict__ W, i
 
 cudaError_t wait_flags_launch(cudaStream_t s, uint32_t* flags, int n, int* status)
 {
+    count_launch();
     wait_flags_kernel<<<1, 32, 0, s>>>(flags, n, status);
     return cudaGetLastError();
 }
@@ -171,6 +172,7 @@ extern "C" int spb_spmm_bitmap_v3_allgather(void* stream, const uint16_t* Compre
     if (e != cudaSuccess || fused) return (int)e;
     const size_t mn = (size_t)M_shard * N_Global;
     const unsigned blocks = (unsigned)((mn / 8 + 255) / 256);
+    spb::count_launch();
     spb::splitk_reduce_gather_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(g, Reduction_Workspace, M_shard, mn, Split_K,
                                                                              M_full, row_offset);
     return (int)cudaGetLastError();

@@ -70,6 +70,7 @@ cudaError_t splitk_reduce(cudaStream_t s, uint16_t* C, const uint16_t* ws, int M
     const size_t threads = mn / 8;
     if (threads == 0) return cudaSuccess;
     const unsigned blocks = (unsigned)((threads + 255) / 256);
+    count_launch();
     if (ep.any() || wait_flags)
         splitk_reduce_kernel<true><<<blocks, 256, 0, s>>>(C, ws, mn, split_k, M, ep, wait_flags, wait_n, status);
     else

@@ -1763,6 +1763,7 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    count_launch();
     return cudaLaunchKernelEx(&cfg, kernel, p, tmap);
 }
 

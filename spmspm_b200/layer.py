@@ -202,8 +202,12 @@ def generate_timed(layer, prompt_len, new_tokens, steps=1, warmup=1, use_graph=T
     with torch.cuda.stream(stream):
         for _ in range(max(warmup, 1)):
             layer.reset()
+            n0 = api.launch_count()
             layer.forward(xp, prompt_len)
+            n1 = api.launch_count()
             layer.forward(xd, 1)
+            # kernels of the SpMM library in one prefill pass and in one decode step (torch's and NCCL's not counted)
+            layer.launches = (n1 - n0, api.launch_count() - n1)
     stream.synchronize()
     if use_graph:
         try:
