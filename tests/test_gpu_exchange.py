@@ -161,3 +161,24 @@ def test_two_ranks_over_symmetric_memory(lib_built, tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     for rank in (0, 1):
         assert (tmp_path / f"result_{rank}").read_text() == "0"
+
+
+def test_wait_that_runs_out_sets_the_status_word_and_leaves_the_context_usable(lib_built):
+    """A rank that never sends: the flag wait gives up after its bounded number of polls (about half a second),
+    reports through the device status word, and the next call works.  Nothing faults or hangs."""
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import spmspm_b200 as sp
+    sp.reset_device_status()
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda")      # two ranks: nobody ever writes entries 0 and 1
+    sp.wait_flags(flags, 2)
+    torch.cuda.synchronize()
+    assert sp.device_status() == 1                                 # kStatusWaitTimeout
+    assert flags.cpu().tolist() == [0, 0, 0, 1]                    # the wait was counted, nothing arrived
+    sp.reset_device_status()
+    assert sp.device_status() == 0
+    A = make_sparse(256, 512, 0.6, seed=77)
+    B = torch.from_numpy(make_dense(16, 512, seed=78)).cuda()
+    got = sp.spmm(sp.encode_device(torch.from_numpy(A).cuda()), B, split_k=1).cpu().numpy().astype(np.float32)
+    ref = oracle.gemm_f32(A, B.cpu().numpy())
+    assert float(np.abs(got - ref).max()) <= 1e-2 * float(np.abs(ref).max())
+    assert sp.device_status() == 0
