@@ -99,6 +99,28 @@ int spb_load_bin_files(const char* val, const char* gtile, const char* mtile, co
                        const char* sizes, int M, int K, uint16_t** vals_out, int** mtile_out, int** gtile_out,
                        uint64_t** bitmap_out, int* max_nnz_out, int* val_count_out);
 
+/*
+ * The fork's extension: a bitmap-compressed SECOND operand (reference csrc/spmm_test_utils.h:523-652,
+ * InitSparseMatrixA_bitmap_v6_B as called at csrc/spmm_test.cu:205, and the 19-argument
+ * SpMM_SplitK_API_bitmap_v3 of csrc/SpMM_API.cuh:47-53).  The layout differs from the weight's: 64 x 64 global
+ * tiles in row-major order, inside each the 16 x 16 median tiles column by column (16 median offsets per global
+ * tile), inside those the four 8 x 8 tiles row-major; bitmaps, zero padding to 8 values per global tile and max_nnz
+ * as for the weight.  spb_encode_b_host encodes a row-major [rows][cols] fp16 matrix on the GPU and returns host
+ * arrays like spb_encode_host (mtile holds 16 * G ints).  spb_decode_operand_b expands such a matrix into dense fp16
+ * [rows][cols] on the device.  spb_spmspm_bitmap_v3 is the SpMM with the activations given in that form: the
+ * compressed B describes the stored [N_Global][K_Global] matrix (N_Global, K_Global multiples of 64); it is expanded
+ * into memory taken from the stream's pool (cudaMallocAsync / cudaFreeAsync: asynchronous, legal under capture) and
+ * the SpMM then runs as spb_spmm_bitmap_v3.  Corrupt offsets set the device status word and expand to zeros.
+ */
+int spb_encode_b_host(const uint16_t* B_h, int rows, int cols, uint16_t** vals, int** tile_nnz, int** mtile, int** gtile,
+                      uint64_t** bitmap, int* max_nnz);
+int spb_decode_operand_b(void* stream, const uint16_t* Compressed_B, const int* TileOffsets_B, const uint64_t* bitmap_B,
+                         int rows, int cols, uint16_t* dense_out);
+int spb_spmspm_bitmap_v3(void* stream, const uint16_t* Compressed_A, const int* TileOffsets, const int* TileOffsets_Median,
+                         const uint64_t* bitmap, const int* max_nnz_intile, const uint16_t* Compressed_B,
+                         const int* TileOffsets_B, const uint64_t* bitmap_B, uint16_t* C, int M_Global, int N_Global,
+                         int K_Global, uint16_t* Reduction_Workspace, int Split_K);
+
 /* --------------------------------------------------------------------- SpMM */
 
 /*

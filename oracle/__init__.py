@@ -26,7 +26,8 @@ def build(force=False):
         subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, capture_output=True)
     # REF_DIR (the csrc directory of a checkout of the reference) overrides the Makefile's default
     ref_dir = os.environ.get("REF_DIR") or _makefile_ref_dir()
-    if ref_dir and os.path.isdir(ref_dir) and (force or not os.path.exists(_REF) or not os.path.exists(_REF_SPMM)):
+    if ref_dir and os.path.isdir(ref_dir) and (force or not os.path.exists(_REF) or not os.path.exists(_REF_SPMM)
+                                                     or not os.path.exists(os.path.join(_HERE, "_ref", "libref_encoder_b.so"))):
         subprocess.run(["make", "-C", _HERE, "ref", f"REF_DIR={ref_dir}"], check=True, capture_output=True)
 
 
@@ -139,6 +140,72 @@ def encode(A):
     assert g == G
     n = int(gtile[G])
     return Encoded(M, K, vals[:n].copy(), tile_nnz[:M * K // 64], mtile[:4 * G], gtile, bitmap[:M * K // 64], mx.value)
+
+
+_REF_B = os.path.join(_HERE, "_ref", "libref_encoder_b.so")
+_ref_b = None
+
+
+def have_ref_b():
+    return os.path.exists(_REF_B)
+
+
+def encode_b(A):
+    """oracle.c restatement of the fork's encoder for a compressed second operand (InitSparseMatrixA_bitmap_v6_B)."""
+    A = _as_u16(A)
+    M, K = A.shape
+    assert M % 64 == 0 and K % 64 == 0
+    G = (M // 64) * (K // 64)
+    vals = np.empty(M * K + 8 * G + 8, np.uint16)
+    tile_nnz = np.empty(max(M * K // 64, 1), np.int32)
+    mtile = np.empty(max(16 * G, 1), np.int32)
+    gtile = np.empty(G + 1, np.int32)
+    bitmap = np.empty(max(M * K // 64, 1), np.uint64)
+    mx = ctypes.c_int(0)
+    fn = lib().oracle_encode_bitmap_v6_b
+    fn.restype = ctypes.c_int
+    g = fn(_p(A, _u16p), M, K, _p(vals, _u16p), _p(tile_nnz, _i32p), _p(mtile, _i32p), _p(gtile, _i32p), _p(bitmap, _u64p),
+           ctypes.byref(mx))
+    assert g == G
+    n = int(gtile[G])
+    return Encoded(M, K, vals[:n].copy(), tile_nnz[:M * K // 64], mtile[:16 * G], gtile, bitmap[:M * K // 64], mx.value)
+
+
+def decode_b(enc):
+    """Dense [M,K] uint16 image of a matrix in the second-operand layout."""
+    out = np.empty((enc.M, enc.K), np.uint16)
+    fn = lib().oracle_decode_bitmap_v6_b
+    fn.restype = None
+    fn(_p(np.ascontiguousarray(enc.vals if enc.vals.size else np.zeros(1, np.uint16)), _u16p), _p(enc.gtile, _i32p),
+       _p(enc.bitmap, _u64p), enc.M, enc.K, _p(out, _u16p))
+    return out
+
+
+def ref_encode_b(A):
+    """The reference's own InitSparseMatrixA_bitmap_v6_B (compiled into oracle/_ref)."""
+    global _ref_b
+    A = _as_u16(A)
+    M, K = A.shape
+    G = (M // 64) * (K // 64)
+    if _ref_b is None:
+        _ref_b = ctypes.CDLL(_REF_B)
+        _ref_b.ref_encode_bitmap_v6_b.restype = ctypes.c_int
+        _ref_b.ref_b_free.argtypes = [ctypes.c_void_p]
+    vals, tn, mt, gt, bm = _u16p(), _i32p(), _i32p(), _i32p(), _u64p()
+    mx = ctypes.c_int(0)
+    g = _ref_b.ref_encode_bitmap_v6_b(_p(A, _u16p), M, K, ctypes.byref(vals), ctypes.byref(tn), ctypes.byref(mt),
+                                      ctypes.byref(gt), ctypes.byref(bm), ctypes.byref(mx))
+    assert g == G
+    gtile = np.ctypeslib.as_array(gt, (G + 1,)).copy()
+    n = int(gtile[G])
+    nt = M * K // 64
+    out = Encoded(M, K, (np.ctypeslib.as_array(vals, (n,)).copy() if n else np.zeros(0, np.uint16)),
+                  np.ctypeslib.as_array(tn, (max(nt, 1),))[:nt].copy(),
+                  np.ctypeslib.as_array(mt, (max(16 * G, 1),))[:16 * G].copy(), gtile,
+                  np.ctypeslib.as_array(bm, (max(nt, 1),))[:nt].copy(), mx.value)
+    for p in (vals, tn, mt, gt, bm):
+        _ref_b.ref_b_free(ctypes.cast(p, ctypes.c_void_p))
+    return out
 
 
 def ref_encode(A):

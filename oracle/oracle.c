@@ -209,6 +209,93 @@ void oracle_decode_bitmap_v3(const uint16_t *vals, const int *mtile, const int *
         }
 }
 
+/* ---------------------------------------------- second-operand layout ---- */
+
+/*
+ * Position of the t-th 8x8 tile inside a 64x64 global tile in the order of the fork's encoder for a compressed
+ * second operand, InitSparseMatrixA_bitmap_v6_B (csrc/spmm_test_utils.h:523-652) with the tile shape its caller
+ * passes (8,16,64,8,16,64; csrc/spmm_test.cu:205): median tiles of 16 x 16, walked column by column (:566-567:
+ * median_tile_k outer, median_tile_m inner); inside a median tile the four 8x8 tiles row-major (:575-578: i = row
+ * half outer, j = column half inner).
+ */
+static void tile_origin_b(int t, int *row, int *col)
+{
+    int mk = t >> 4, mm = (t >> 2) & 3, i = (t >> 1) & 1, j = t & 1;
+    *row = 16 * mm + 8 * i;
+    *col = 16 * mk + 8 * j;
+}
+
+/*
+ * Restates InitSparseMatrixA_bitmap_v6_B (csrc/spmm_test_utils.h:523-652).  Input row-major [M][K].  Outputs as
+ * oracle_encode_bitmap_v3 except mtile: 16 ints per global tile, the first 0 (:564), then the running count after
+ * every median tile but the last (:617-621).  Zero test (:589), bit position (:590), padding to 8 (:626-630),
+ * max_nnz (:634-636), global offsets (:641-645) as in the weight encoder.
+ */
+int oracle_encode_bitmap_v6_b(const uint16_t *A, int M, int K, uint16_t *vals, int *tile_nnz, int *mtile, int *gtile,
+                              uint64_t *bitmap, int *max_nnz)
+{
+    int GM = M / 64, GK = K / 64, G = GM * GK, val_count = 0, mx = 0;
+    gtile[0] = 0;
+    for (int gm = 0; gm < GM; ++gm)
+        for (int gk = 0; gk < GK; ++gk) {
+            int g = gm * GK + gk, in_gtile = 0;
+            for (int t = 0; t < 64; ++t) {
+                if ((t & 3) == 0)
+                    mtile[16 * g + (t >> 2)] = in_gtile;
+                int r0, c0;
+                tile_origin_b(t, &r0, &c0);
+                uint64_t bm = 0;
+                int cnt = 0;
+                for (int r = 0; r < 8; ++r) {
+                    const uint16_t *src = A + (size_t)(gm * 64 + r0 + r) * K + gk * 64 + c0;
+                    for (int c = 0; c < 8; ++c) {
+                        uint16_t h = src[c];
+                        if ((h & 0x7fffu) != 0) {
+                            bm |= 1ull << (r * 8 + c);
+                            vals[val_count++] = h;
+                            cnt++;
+                        }
+                    }
+                }
+                bitmap[(size_t)g * 64 + t] = bm;
+                tile_nnz[(size_t)g * 64 + t] = cnt;
+                in_gtile += cnt;
+            }
+            while (in_gtile & 7) {
+                vals[val_count++] = 0;
+                in_gtile++;
+            }
+            if (in_gtile > mx)
+                mx = in_gtile;
+            gtile[g + 1] = val_count;
+        }
+    *max_nnz = mx;
+    return G;
+}
+
+/* Inverse of the above: the tiles of a global tile are consecutive in storage order, element (r,c) of a tile sits
+ * popcount(bitmap & ((1 << (8r+c)) - 1)) values after the tile's start. */
+void oracle_decode_bitmap_v6_b(const uint16_t *vals, const int *gtile, const uint64_t *bitmap, int M, int K,
+                               uint16_t *A_out)
+{
+    int GM = M / 64, GK = K / 64;
+    for (int gm = 0; gm < GM; ++gm)
+        for (int gk = 0; gk < GK; ++gk) {
+            int g = gm * GK + gk, pos = gtile[g];
+            for (int t = 0; t < 64; ++t) {
+                int r0, c0;
+                tile_origin_b(t, &r0, &c0);
+                uint64_t bm = bitmap[(size_t)g * 64 + t];
+                for (int b = 0; b < 64; ++b) {
+                    uint16_t h = 0;
+                    if ((bm >> b) & 1ull)
+                        h = vals[pos++];
+                    A_out[(size_t)(gm * 64 + r0 + (b >> 3)) * K + gk * 64 + c0 + (b & 7)] = h;
+                }
+            }
+        }
+}
+
 /* --------------------------------------------------------------- GEMM ---- */
 
 /*

@@ -21,6 +21,11 @@ SIGNATURES = {
     "spb_last_error": (ctypes.c_char_p, []),
     "spb_encode_host": (ctypes.c_int, [_vp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_u16p), ctypes.POINTER(_i32p),
                                        ctypes.POINTER(_i32p), ctypes.POINTER(_i32p), ctypes.POINTER(_u64p), _i32p]),
+    "spb_encode_b_host": (ctypes.c_int, [_vp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_u16p), ctypes.POINTER(_i32p),
+                                         ctypes.POINTER(_i32p), ctypes.POINTER(_i32p), ctypes.POINTER(_u64p), _i32p]),
+    "spb_decode_operand_b": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int, _vp]),
+    "spb_spmspm_bitmap_v3": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,
+                                            ctypes.c_int, _vp, ctypes.c_int]),
     "spb_free_host": (None, [_vp]),
     "spb_encode_scratch_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.c_int]),
     "spb_encode_device": (ctypes.c_int, [_vp, _vp, ctypes.c_int, ctypes.c_int, _vp, ctypes.c_size_t, _vp, _vp, _vp,
@@ -57,6 +62,9 @@ SIGNATURES = {
 MANGLED = [
     "_Z25SpMM_SplitK_API_bitmap_v3P11CUstream_stPK6__halfS3_PKiS5_PKmS5_S3_PS1_iiiS8_i",
     "_Z24InitSparseMatrixA_bitmapP6__halfiiiiiiiiPS0_PPiS3_S3_PPmRi",
+    # the fork's forms with a compressed second operand (csrc/SpMM_API.cuh:47-53, csrc/spmm_test_utils.h:523)
+    "_Z25SpMM_SplitK_API_bitmap_v3P11CUstream_stPK6__halfS3_PKiS5_PKmS5_S3_S3_S5_S5_S7_S5_PS1_iiiS8_i",
+    "_Z29InitSparseMatrixA_bitmap_v6_BP6__halfiiiiiiiiPS0_PPiS3_S3_PPmRi",
 ]
 
 NOALLOC_MAX_SCRATCH_BYTES = 16 << 20  # SPB_NOALLOC_MAX_SCRATCH_BYTES in include/spmm_b200.h

@@ -52,7 +52,13 @@ class HostEncoded:
         return (self.M // 64) * (self.K // 64)
 
 
-def init_sparse_matrix_a_bitmap(A_h):
+def init_sparse_matrix_a_bitmap_v6_b(B_h):
+    """Encode a host fp16 matrix [rows, cols] in the fork's second-operand layout (InitSparseMatrixA_bitmap_v6_B,
+    csrc/spmm_test_utils.h:523-652) on the GPU; HostEncoded.mtile then holds 16 offsets per global tile."""
+    return init_sparse_matrix_a_bitmap(B_h, _second_operand=True)
+
+
+def init_sparse_matrix_a_bitmap(A_h, _second_operand=False):
     """Encode a host fp16 matrix [M,K] on the GPU; returns HostEncoded (bit-identical to the reference)."""
     A_h = np.ascontiguousarray(A_h)
     if A_h.dtype == np.float16:
@@ -64,8 +70,9 @@ def init_sparse_matrix_a_bitmap(A_h):
     u16p, i32p, u64p = ctypes.POINTER(ctypes.c_uint16), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_uint64)
     vals, tn, mt, gt, bm = u16p(), i32p(), i32p(), i32p(), u64p()
     mx = ctypes.c_int(0)
-    g = lib.spb_encode_host(ctypes.c_void_p(A_h.ctypes.data), M, K, ctypes.byref(vals), ctypes.byref(tn),
-                            ctypes.byref(mt), ctypes.byref(gt), ctypes.byref(bm), ctypes.byref(mx))
+    fn = lib.spb_encode_b_host if _second_operand else lib.spb_encode_host
+    g = fn(ctypes.c_void_p(A_h.ctypes.data), M, K, ctypes.byref(vals), ctypes.byref(tn),
+           ctypes.byref(mt), ctypes.byref(gt), ctypes.byref(bm), ctypes.byref(mx))
     try:
         if g < 0:
             raise SpmmError(f"InitSparseMatrixA_bitmap failed ({g}): {_lib.last_error()}")
@@ -76,7 +83,7 @@ def init_sparse_matrix_a_bitmap(A_h):
             M, K,
             np.ctypeslib.as_array(vals, (n,)).copy() if n else np.zeros(0, np.uint16),
             np.ctypeslib.as_array(tn, (nt,)).copy(),
-            np.ctypeslib.as_array(mt, (4 * g,)).copy(),
+            np.ctypeslib.as_array(mt, ((16 if _second_operand else 4) * g,)).copy(),
             gtile,
             np.ctypeslib.as_array(bm, (nt,)).copy(),
             mx.value)
@@ -365,6 +372,39 @@ def linear(W: BitmapMatrix, B, bias=None, residual=None, activation=ACT_NONE, sp
                                                 _ptr(residual) if residual is not None else None, int(activation),
                                                 _ptr(workspace) if workspace is not None else None, split_k)
     _check(code, "spb_linear_bitmap_v3")
+    return out
+
+
+def decode_operand_b(Bc: BitmapMatrix, out=None, stream=None):
+    """spb_decode_operand_b: a matrix in the second-operand layout (to_device of init_sparse_matrix_a_bitmap_v6_b)
+    expanded to dense fp16 [rows, cols]."""
+    if out is None:
+        out = torch.empty((Bc.M, Bc.K), dtype=torch.float16, device=Bc.vals.device)
+    with torch.cuda.device(out.device):
+        code = _lib.load().spb_decode_operand_b(_stream_ptr(stream), _ptr(Bc.vals), _ptr(Bc.gtile), _ptr(Bc.bitmap), Bc.M, Bc.K,
+                                                _ptr(out))
+    _check(code, "spb_decode_operand_b")
+    return out
+
+
+def spmspm(W: BitmapMatrix, Bc: BitmapMatrix, split_k=None, out=None, workspace=None, stream=None):
+    """spb_spmspm_bitmap_v3: C[N,M] with both operands bitmap-compressed; Bc encodes the stored [N,K] activations in
+    the second-operand layout."""
+    if Bc.K != W.K:
+        raise SpmmError("the compressed second operand must be [N,K]")
+    N = Bc.M
+    if split_k is None:
+        split_k = suggest_split_k(W.M, N, W.K)
+    if out is None:
+        out = torch.empty((N, W.M), dtype=torch.float16, device=W.vals.device)
+    if split_k > 1 and workspace is None:
+        workspace = torch.empty(split_k * N * W.M, dtype=torch.float16, device=W.vals.device)
+    with torch.cuda.device(W.vals.device):
+        _init_if_possible(stream)
+        code = _lib.load().spb_spmspm_bitmap_v3(_stream_ptr(stream), _ptr(W.vals), _ptr(W.gtile), _ptr(W.mtile), _ptr(W.bitmap),
+                                                _ptr(W.max_nnz), _ptr(Bc.vals), _ptr(Bc.gtile), _ptr(Bc.bitmap), _ptr(out),
+                                                W.M, N, W.K, _ptr(workspace) if workspace is not None else None, split_k)
+    _check(code, "spb_spmspm_bitmap_v3")
     return out
 
 

@@ -127,6 +127,36 @@ static cudaError_t spmm_checked(cudaStream_t stream, const uint16_t* vals, const
     return splitk_reduce(stream, C, ws, M, N, split_k, ep);
 }
 
+// SpMSpM: the compressed second operand (the stored [N][K] activation matrix in the second-operand layout) is
+// expanded into a dense array from the stream's memory pool, then the SpMM runs as for a dense B.
+static cudaError_t spmspm_checked(cudaStream_t stream, const uint16_t* vals, const int* gtile, const int* mtile,
+                                  const uint64_t* bitmap, const int* max_nnz, const uint16_t* vals_b, const int* gtile_b,
+                                  const uint64_t* bitmap_b, uint16_t* C, int M, int N, int K, uint16_t* ws, int split_k)
+{
+    if (!vals_b || !gtile_b || !bitmap_b) {
+        set_error("SpMSpM: null pointer for the compressed second operand");
+        return cudaErrorInvalidValue;
+    }
+    if (N <= 0 || K <= 0 || (N % 64) || (K % 64)) {
+        set_error("SpMSpM: N and K must be positive multiples of 64 (the second operand is tiled 64 x 64), N=%d K=%d", N, K);
+        return cudaErrorInvalidValue;
+    }
+    int* status = nullptr;
+    cudaError_t e = device_status_ptr(&status);
+    if (e != cudaSuccess) return e;
+    void* dense = nullptr;
+    e = cudaMallocAsync(&dense, (size_t)N * K * 2, stream);
+    if (e != cudaSuccess) {
+        set_error("SpMSpM: no memory for the expanded second operand (%zu bytes)", (size_t)N * K * 2);
+        return e;
+    }
+    e = decode_operand_b(stream, vals_b, gtile_b, bitmap_b, N, K, (uint16_t*)dense, status);
+    if (e == cudaSuccess)
+        e = spmm_checked(stream, vals, gtile, mtile, bitmap, max_nnz, (const uint16_t*)dense, C, M, N, K, ws, split_k);
+    const cudaError_t f = cudaFreeAsync(dense, stream);
+    return e != cudaSuccess ? e : f;
+}
+
 struct DevBuf {
     void* p = nullptr;
     ~DevBuf()
@@ -137,8 +167,9 @@ struct DevBuf {
 };
 
 static int encode_host_impl(const uint16_t* A_h, int M, int K, uint16_t** vals, int** tile_nnz, int** mtile,
-                            int** gtile, uint64_t** bitmap, int* max_nnz)
+                            int** gtile, uint64_t** bitmap, int* max_nnz, int fmt = kFmtWeight)
 {
+    const size_t mt_per_g = fmt == kFmtWeight ? 4 : 16;   // median offsets per global tile
     if (!A_h || M <= 0 || K <= 0 || (M % 64) || (K % 64)) {
         set_error("encode: M and K must be positive multiples of 64 (M=%d K=%d)", M, K);
         return -(1000 + (int)cudaErrorInvalidValue);
@@ -166,7 +197,7 @@ static int encode_host_impl(const uint16_t* A_h, int M, int K, uint16_t** vals, 
     DevBuf dA, dtn, dmt, dgt, dbm, dmx, dscr, dvals, dst;
     SPB_TRY(dA.alloc(MK * 2));
     SPB_TRY(dtn.alloc(nt * 4));
-    SPB_TRY(dmt.alloc(G * 16));
+    SPB_TRY(dmt.alloc(G * mt_per_g * 4));
     SPB_TRY(dgt.alloc((G + 1) * 4));
     SPB_TRY(dbm.alloc(nt * 8));
     SPB_TRY(dmx.alloc(4));
@@ -176,7 +207,7 @@ static int encode_host_impl(const uint16_t* A_h, int M, int K, uint16_t** vals, 
     SPB_TRY(cudaMemcpyAsync(dA.p, A_h, MK * 2, cudaMemcpyHostToDevice, s));
     SPB_TRY(cudaMemsetAsync(dst.p, 0, 4, s));
     SPB_TRY(encode_count_and_scan(s, (const uint16_t*)dA.p, M, K, (int*)dtn.p, (int*)dmt.p, (int*)dgt.p,
-                                  (uint64_t*)dbm.p, (int*)dmx.p, dscr.p));
+                                  (uint64_t*)dbm.p, (int*)dmx.p, dscr.p, fmt));
     int val_count = 0, mx = 0;
     SPB_TRY(cudaMemcpyAsync(&val_count, (int*)dgt.p + G, 4, cudaMemcpyDeviceToHost, s));
     SPB_TRY(cudaMemcpyAsync(&mx, dmx.p, 4, cudaMemcpyDeviceToHost, s));
@@ -185,10 +216,10 @@ static int encode_host_impl(const uint16_t* A_h, int M, int K, uint16_t** vals, 
     if (!*vals) return -1;
     SPB_TRY(dvals.alloc((size_t)val_count * 2));
     SPB_TRY(encode_pack(s, (const uint16_t*)dA.p, M, K, (const int*)dgt.p, (const uint64_t*)dbm.p,
-                        (uint16_t*)dvals.p, (size_t)val_count, (int*)dst.p));
+                        (uint16_t*)dvals.p, (size_t)val_count, (int*)dst.p, fmt));
     SPB_TRY(cudaMemcpyAsync(*vals, dvals.p, (size_t)val_count * 2, cudaMemcpyDeviceToHost, s));
     SPB_TRY(cudaMemcpyAsync(*tile_nnz, dtn.p, nt * 4, cudaMemcpyDeviceToHost, s));
-    SPB_TRY(cudaMemcpyAsync(*mtile, dmt.p, G * 16, cudaMemcpyDeviceToHost, s));
+    SPB_TRY(cudaMemcpyAsync(*mtile, dmt.p, G * mt_per_g * 4, cudaMemcpyDeviceToHost, s));
     SPB_TRY(cudaMemcpyAsync(*gtile, dgt.p, (G + 1) * 4, cudaMemcpyDeviceToHost, s));
     SPB_TRY(cudaMemcpyAsync(*bitmap, dbm.p, nt * 8, cudaMemcpyDeviceToHost, s));
     SPB_TRY(cudaStreamSynchronize(s));
@@ -355,6 +386,26 @@ int spb_encode_host(const uint16_t* A_h, int M, int K, uint16_t** vals, int** ti
     return spb::encode_host_impl(A_h, M, K, vals, tile_nnz, mtile, gtile, bitmap, max_nnz);
 }
 
+int spb_encode_b_host(const uint16_t* B_h, int rows, int cols, uint16_t** vals, int** tile_nnz, int** mtile, int** gtile,
+                      uint64_t** bitmap, int* max_nnz)
+{
+    if (!vals || !tile_nnz || !mtile || !gtile || !bitmap || !max_nnz) {
+        spb::set_error("encode: null output pointer");
+        return -(1000 + (int)cudaErrorInvalidValue);
+    }
+    return spb::encode_host_impl(B_h, rows, cols, vals, tile_nnz, mtile, gtile, bitmap, max_nnz, spb::kFmtOperandB);
+}
+
+int spb_spmspm_bitmap_v3(void* stream, const uint16_t* Compressed_A, const int* TileOffsets, const int* TileOffsets_Median,
+                         const uint64_t* bitmap, const int* max_nnz_intile, const uint16_t* Compressed_B,
+                         const int* TileOffsets_B, const uint64_t* bitmap_B, uint16_t* C, int M_Global, int N_Global,
+                         int K_Global, uint16_t* Reduction_Workspace, int Split_K)
+{
+    return (int)spb::spmspm_checked((cudaStream_t)stream, Compressed_A, TileOffsets, TileOffsets_Median, bitmap,
+                                    max_nnz_intile, Compressed_B, TileOffsets_B, bitmap_B, C, M_Global, N_Global, K_Global,
+                                    Reduction_Workspace, Split_K);
+}
+
 void spb_free_host(void* p) { free(p); }
 
 size_t spb_encode_scratch_bytes(int M, int K) { return spb::encode_scratch_bytes(M, K); }
@@ -514,6 +565,47 @@ int InitSparseMatrixA_bitmap(half* A_h, int M, int K, int tile_M, int tile_M_med
     int g = spb::encode_host_impl(reinterpret_cast<const uint16_t*>(A_h), M, K,
                                   reinterpret_cast<uint16_t**>(Compressed_Val), TileOffsets, TileOffsets_median,
                                   TileOffsets_global, bitmap, &mx);
+    max_nnz_count = mx;
+    return g < 0 ? -1 : g;
+}
+
+// The fork's extension: the second operand compressed too (reference csrc/SpMM_API.cuh:47-53, 19 arguments).  The
+// dense B passed beside its compressed form is ignored, like A.  The compressed B describes the stored [N][K] matrix
+// (what InitSparseMatrixA_bitmap_v6_B makes of it with M = N_Global, K = K_Global).
+cudaError_t SpMM_SplitK_API_bitmap_v3(cudaStream_t stream, const half* A, const half* Compressed_A, const int* TileOffsets,
+                                      const int* TileOffsets_Median, const uint64_t* bitmap, const int* max_nnz_intile,
+                                      const half* B, const half* Compressed_B, const int* TileOffsets_B,
+                                      const int* TileOffsets_Median_B, const uint64_t* bitmap_B,
+                                      const int* max_nnz_intile_B, half* C, const int M_Global, const int N_Global,
+                                      const int K_Global, half* Reduction_Workspace, int Split_K)
+{
+    (void)A;
+    (void)B;
+    (void)TileOffsets_Median_B;   // the expansion takes the tile starts from the bitmaps
+    (void)max_nnz_intile_B;
+    cudaError_t e = spb::spmspm_checked(stream, reinterpret_cast<const uint16_t*>(Compressed_A), TileOffsets, TileOffsets_Median,
+                                        bitmap, max_nnz_intile, reinterpret_cast<const uint16_t*>(Compressed_B), TileOffsets_B,
+                                        bitmap_B, reinterpret_cast<uint16_t*>(C), M_Global, N_Global, K_Global,
+                                        reinterpret_cast<uint16_t*>(Reduction_Workspace), Split_K);
+    if (e == cudaErrorInvalidValue || e == cudaErrorMisalignedAddress) printf("MM_Sparse_API Error: %s\n", spb::g_err);
+    return e;
+}
+
+// reference csrc/spmm_test_utils.h:523-652; only the tile shape its caller passes (csrc/spmm_test.cu:205) is supported
+int InitSparseMatrixA_bitmap_v6_B(half* A_h, int M, int K, int tile_M, int tile_M_median, int tile_M_global, int tile_K,
+                                  int tile_K_median, int tile_K_global, half** Compressed_Val, int** TileOffsets,
+                                  int** TileOffsets_median, int** TileOffsets_global, uint64_t** bitmap, int& max_nnz_count)
+{
+    if (tile_M != 8 || tile_M_median != 16 || tile_M_global != 64 || tile_K != 8 || tile_K_median != 16 ||
+        tile_K_global != 64) {
+        spb::set_error("InitSparseMatrixA_bitmap_v6_B: only the tile shape (8,16,64,8,16,64) is supported");
+        printf("InitSparseMatrixA_bitmap_v6_B Error: %s\n", spb::g_err);
+        return -1;
+    }
+    int mx = 0;
+    int g = spb::encode_host_impl(reinterpret_cast<const uint16_t*>(A_h), M, K,
+                                  reinterpret_cast<uint16_t**>(Compressed_Val), TileOffsets, TileOffsets_median,
+                                  TileOffsets_global, bitmap, &mx, spb::kFmtOperandB);
     max_nnz_count = mx;
     return g < 0 ? -1 : g;
 }

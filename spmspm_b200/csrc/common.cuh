@@ -21,10 +21,16 @@ cudaError_t device_status_ptr(int** out);
 size_t encode_scratch_bytes(int M, int K);
 // Pass 1+2: bitmaps, per-tile counts, median offsets, global offsets, max.
 cudaError_t encode_count_and_scan(cudaStream_t s, const uint16_t* A, int M, int K, int* tile_nnz, int* mtile,
-                                  int* gtile, uint64_t* bitmap, int* max_nnz, void* scratch);
+                                  int* gtile, uint64_t* bitmap, int* max_nnz, void* scratch, int fmt = 0);
 // Pass 3: packed values.
 cudaError_t encode_pack(cudaStream_t s, const uint16_t* A, int M, int K, const int* gtile, const uint64_t* bitmap,
-                        uint16_t* vals, size_t vals_capacity, int* status);
+                        uint16_t* vals, size_t vals_capacity, int* status, int fmt = 0);
+// fmt: 0 = the weight layout (InitSparseMatrixA_bitmap), 1 = the fork's layout for a compressed second operand
+// (InitSparseMatrixA_bitmap_v6_B: 16 median offsets per global tile, mtile holds 16 * G ints).
+constexpr int kFmtWeight = 0, kFmtOperandB = 1;
+// Expands a matrix [rows][cols] in the second-operand layout into dense fp16 (sparse_b.cu).
+cudaError_t decode_operand_b(cudaStream_t s, const uint16_t* vals, const int* gtile, const uint64_t* bitmap, int rows,
+                             int cols, uint16_t* dense, int* status);
 
 // ---- split-K reduction (reduction.cu) --------------------------------------
 // Element-wise tail of a linear layer (see epilogue.cuh): bias [M] fp16 or null, residual in the layout of the

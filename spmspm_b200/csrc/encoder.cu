@@ -20,9 +20,15 @@ constexpr int kEncThreads = 256;
 // Tile index, inside its 64x64 global tile, of the 8x8 tile holding element
 // (row, 8*cc): median tile row>>4, 16-column group cc>>1, then the 2x2 order of
 // reference csrc/SpMM_API.cuh:170-176 (column half outer, row half inner).
+// kFmt 1 is the layout of the fork's encoder for the second operand, InitSparseMatrixA_bitmap_v6_B
+// (reference csrc/spmm_test_utils.h:523-652, called with median tiles of 16 x 16): median tiles column-major inside
+// the global tile (16-column step outer, 16-row step inner, :566-567), the 2x2 tiles of a median tile row-major
+// (:575-578), and one median offset per 16x16 median tile (16 per global tile, :564, :617-621).
+template <int kFmt>
 __device__ __forceinline__ int tile_of(int row, int cc)
 {
-    return 16 * (row >> 4) + 4 * (cc >> 1) + 2 * (cc & 1) + ((row >> 3) & 1);
+    if (kFmt == 0) return 16 * (row >> 4) + 4 * (cc >> 1) + 2 * (cc & 1) + ((row >> 3) & 1);
+    return 16 * (cc >> 1) + 4 * (row >> 4) + 2 * ((row >> 3) & 1) + (cc & 1);
 }
 
 // Bit c set when the c-th fp16 of the 16-byte segment is kept.  The reference
@@ -64,6 +70,7 @@ __device__ __forceinline__ int scan64(int v, int* warp_total)
     return x;
 }
 
+template <int kFmt>
 __global__ void __launch_bounds__(kEncThreads)
 encode_count_kernel(const uint16_t* __restrict__ A, int K, int GK, int* __restrict__ tile_nnz,
                     int* __restrict__ mtile, int* __restrict__ gcount, uint64_t* __restrict__ bitmap,
@@ -77,7 +84,7 @@ encode_count_kernel(const uint16_t* __restrict__ A, int K, int GK, int* __restri
     for (int u = 0; u < 2; ++u) {
         const int row = u * 32 + (t >> 3), cc = t & 7;
         const uint4 v = load_segment(A, K, gm, gk, row, cc);
-        rowmask[tile_of(row, cc) * 8 + (row & 7)] = (uint8_t)nonzero_mask(v);
+        rowmask[tile_of<kFmt>(row, cc) * 8 + (row & 7)] = (uint8_t)nonzero_mask(v);
     }
     __syncthreads();
     if (t < 64) {
@@ -86,7 +93,11 @@ encode_count_kernel(const uint16_t* __restrict__ A, int K, int GK, int* __restri
         bitmap[(size_t)g * 64 + t] = bm;
         tile_nnz[(size_t)g * 64 + t] = cnt;
         const int incl = scan64(cnt, &warp_total);
-        if ((t & 15) == 0) mtile[(size_t)g * 4 + (t >> 4)] = incl - cnt;
+        if (kFmt == 0) {
+            if ((t & 15) == 0) mtile[(size_t)g * 4 + (t >> 4)] = incl - cnt;
+        } else {
+            if ((t & 3) == 0) mtile[(size_t)g * 16 + (t >> 2)] = incl - cnt;
+        }
         if (t == 63) {
             const int padded = (incl + 7) & ~7;  // reference csrc/SpMM_API.cuh:216-220
             gcount[g] = padded;
@@ -135,6 +146,7 @@ __global__ void __launch_bounds__(1024) encode_scan_kernel(const int* __restrict
     }
 }
 
+template <int kFmt>
 __global__ void __launch_bounds__(kEncThreads)
 encode_pack_kernel(const uint16_t* __restrict__ A, int K, int GK, const int* __restrict__ gtile,
                    uint16_t* __restrict__ vals, size_t capacity, int* __restrict__ status)
@@ -150,7 +162,7 @@ encode_pack_kernel(const uint16_t* __restrict__ A, int K, int GK, const int* __r
     for (int u = 0; u < 2; ++u) {
         const int row = u * 32 + (t >> 3), cc = t & 7;
         v[u] = load_segment(A, K, gm, gk, row, cc);
-        rowmask[tile_of(row, cc) * 8 + (row & 7)] = (uint8_t)nonzero_mask(v[u]);
+        rowmask[tile_of<kFmt>(row, cc) * 8 + (row & 7)] = (uint8_t)nonzero_mask(v[u]);
     }
     __syncthreads();
     if (t < 64) {
@@ -165,7 +177,7 @@ encode_pack_kernel(const uint16_t* __restrict__ A, int K, int GK, const int* __r
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
         const int row = u * 32 + (t >> 3), cc = t & 7, r = row & 7;
-        const int tile = tile_of(row, cc);
+        const int tile = tile_of<kFmt>(row, cc);
         const uint64_t bm = *reinterpret_cast<const uint64_t*>(&rowmask[tile * 8]);
         int off = tstart[tile] + __popcll(bm & ((1ull << (8 * r)) - 1ull));
         const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
@@ -205,25 +217,29 @@ size_t encode_scratch_bytes(int M, int K)
 }
 
 cudaError_t encode_count_and_scan(cudaStream_t s, const uint16_t* A, int M, int K, int* tile_nnz, int* mtile,
-                                  int* gtile, uint64_t* bitmap, int* max_nnz, void* scratch)
+                                  int* gtile, uint64_t* bitmap, int* max_nnz, void* scratch, int fmt)
 {
     const int GK = K / 64, G = (M / 64) * GK;
     count_launch(G > 0 ? 3 : 2);
     encode_init_kernel<<<1, 1, 0, s>>>(max_nnz);
     if (G > 0) {
-        encode_count_kernel<<<G, kEncThreads, 0, s>>>(A, K, GK, tile_nnz, mtile, (int*)scratch, bitmap, max_nnz);
+        if (fmt == 0)
+            encode_count_kernel<0><<<G, kEncThreads, 0, s>>>(A, K, GK, tile_nnz, mtile, (int*)scratch, bitmap, max_nnz);
+        else
+            encode_count_kernel<1><<<G, kEncThreads, 0, s>>>(A, K, GK, tile_nnz, mtile, (int*)scratch, bitmap, max_nnz);
     }
     encode_scan_kernel<<<1, 1024, 0, s>>>((const int*)scratch, gtile, G);
     return cudaGetLastError();
 }
 
 cudaError_t encode_pack(cudaStream_t s, const uint16_t* A, int M, int K, const int* gtile, const uint64_t* bitmap,
-                        uint16_t* vals, size_t vals_capacity, int* status)
+                        uint16_t* vals, size_t vals_capacity, int* status, int fmt)
 {
     (void)bitmap;
     const int GK = K / 64, G = (M / 64) * GK;
     if (G > 0) count_launch();
-    if (G > 0) encode_pack_kernel<<<G, kEncThreads, 0, s>>>(A, K, GK, gtile, vals, vals_capacity, status);
+    if (G > 0 && fmt == 0) encode_pack_kernel<0><<<G, kEncThreads, 0, s>>>(A, K, GK, gtile, vals, vals_capacity, status);
+    if (G > 0 && fmt != 0) encode_pack_kernel<1><<<G, kEncThreads, 0, s>>>(A, K, GK, gtile, vals, vals_capacity, status);
     return cudaGetLastError();
 }
 

@@ -3,7 +3,8 @@
 Run in a container that has the reference sources (oracle/Makefile builds them into
 oracle/_ref):   python tests/golden/make_golden.py
 Each .npz holds the dense input (fp16 bit patterns) and the five arrays plus max_nnz that the
-reference's InitSparseMatrixA_bitmap (csrc/SpMM_API.cuh:112-241) returned for it.
+reference's InitSparseMatrixA_bitmap (csrc/SpMM_API.cuh:112-241) returned for it; operand_b/*.npz hold the same for
+the fork's encoder of a compressed second operand, InitSparseMatrixA_bitmap_v6_B (csrc/spmm_test_utils.h:523-652).
 """
 import os
 import sys
@@ -48,6 +49,13 @@ def main():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), A=A, vals=e.vals, tile_nnz=e.tile_nnz, mtile=e.mtile,
                             gtile=e.gtile, bitmap=e.bitmap, max_nnz=np.int32(e.max_nnz))
         print(name, A.shape, "val_count", e.vals.size, "max_nnz", e.max_nnz)
+    assert oracle.have_ref_b(), "oracle/_ref/libref_encoder_b.so is not built"
+    os.makedirs(os.path.join(HERE, "operand_b"), exist_ok=True)
+    for name, A in cases().items():
+        e = oracle.ref_encode_b(A)
+        np.savez_compressed(os.path.join(HERE, "operand_b", name + ".npz"), A=A, vals=e.vals, tile_nnz=e.tile_nnz,
+                            mtile=e.mtile, gtile=e.gtile, bitmap=e.bitmap, max_nnz=np.int32(e.max_nnz))
+        print("operand_b", name, A.shape, "val_count", e.vals.size, "max_nnz", e.max_nnz)
 
 
 if __name__ == "__main__":
