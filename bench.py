@@ -4,9 +4,16 @@
 A step is one pass over a set of layer-shaped SpMMs.  The default workload is the OPT-13B layer set (four weight
 matrices at 60 % uniform-random sparsity, each multiplied at N = 8, 16 and 32: twelve SpMMs), the configuration
 the headline metric is quoted on; `--workload opt66b_tp` is the OPT-66B set at N = 16 (four SpMMs) whose row shards
-are checked bit for bit against the CPU encoder inside the run.  Inputs are synthetic and seeded.  With more than
-one GPU each weight matrix is split by rows across the ranks (tensor-parallel M-split) and the output rows are
-gathered on every rank, so the total work is fixed ("strong" scaling).
+are checked bit for bit against the CPU encoder inside the run; `--workload opt66b_layer` runs one synthetic OPT-66B
+decoder layer (batch 8, 64 prompt tokens, 128 generated tokens) and reports tokens/s.  Inputs are synthetic and
+seeded.  With more than one GPU each weight matrix is split by rows across the ranks (tensor-parallel M-split) and
+the output rows are gathered on every rank (the layer workload splits as FasterTransformer does: QKV and FC1 by rows,
+out-proj and FC2 by columns with an all-reduce), so the total work is fixed ("strong" scaling).
+
+The JSON line carries: value (device-resident, CUDA events, graph replay over rotating weight copies), e2e (host
+buffers through spmspm_b200.pipeline.HostBatch), roofline (algorithmic bytes / time against the measured HBM copy
+bandwidth; traffic from the committed profiler capture), parity (sampled rows against the fp32 host GEMM; a failure
+exits 1), comparators (dense cuBLAS fp16 and the reference-style mma.sync kernel), cpu_baseline, encoder, clocks.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME | --case M,K,N[,s[,sk]]]
 
