@@ -65,8 +65,9 @@ namespace {
 //   warpgroup 2..: decode groups (one warp per quadrant each)
 // A pipeline stage holds kKT consecutive k-tiles of one 128-row block, one for each of the four decode
 // groups.  (Stages of one or two k-tiles mean more stages in the shared-memory ring and more copies per
-// byte; they measured 1.7x and 1.15x slower.)  Activation tiles wider than 64 columns leave room for two k-tiles
-// per stage only (stage_kt).
+// byte; they measured 1.7x and 1.15x slower: a producer warp spends about 2300 cycles per stage whatever the stage
+// holds, so two-k-tile stages cap the kernel near 0.6 us per k-tile; the 32-column tile ran 108 instead of 83 us with
+// them.)  Activation tiles wider than 64 columns leave room for two k-tiles per stage only (stage_kt).
 constexpr int kKT = 4;
 __host__ __device__ constexpr int stage_kt(int npad) { return npad > 64 ? 2 : 4; }
 #ifndef SPB_GROUPS
@@ -700,7 +701,8 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     // The stage size depends on max_nnz_intile, a load from global memory that takes most of a microsecond.  The
     // load is issued here; what is derived from it (SPB_CARVE) is computed by each role only after the part of
     // its start-up that does not need it (walking to its first work item, fetching the first tile offsets), so
-    // that nobody sits on the load.
+    // that nobody sits on the load.  (Issuing it, and an L2 prefetch of the first tile offsets, before the set-up
+    // instead was measured: no difference.)
     int max_nnz_ld;
     asm volatile("ld.global.cg.s32 %0, [%1];" : "=r"(max_nnz_ld) : "l"(p.max_nnz));
     constexpr uint32_t kBTile = NPAD * 128;
