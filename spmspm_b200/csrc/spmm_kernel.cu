@@ -78,12 +78,10 @@ __host__ __device__ constexpr int stage_kt(int npad) { return npad > 64 ? 2 : 4;
 constexpr int kDecodeGroups = SPB_GROUPS;
 static_assert(kDecodeGroups >= kKT && kDecodeGroups <= 6, "a stage must not give a group two k-tiles; 32 warps at most");
 // A operand blocks in tensor memory (32 columns = one k-tile each), used in turn: k-tile t uses block t % kABlocks.
-// With the accumulators kept to 128 columns there is room for 12: a group that expands kUnit k-tiles per turn can
-// start its next turn while the tensor core still reads the blocks of its last one.
-// Activation tiles of 256 columns need 256 columns of tensor memory for their accumulator, tiles of 128 columns
-// get two accumulators (the epilogue of a work item then overlaps the MMAs of the next): 8 blocks are left.
-constexpr int kABlocks = 12;
-__host__ __device__ constexpr int a_blocks(int npad) { return npad >= 128 ? 8 : 12; }
+// Eight blocks, two per decode group: a group can start its next k-tile while the tensor core still reads its last
+// one.  A power of two, so that block and barrier phase of the t-th k-tile of the CTA's sequence are t % 8 and
+// (t / 8) % 2 with no bookkeeping (twelve blocks with per-block phase bits measured 2 % slower).
+constexpr int kABlocks = 8;
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
@@ -331,13 +329,7 @@ __device__ __forceinline__ bool bar_and_epilogue(bool pred)
         : "memory");
     return r != 0;
 }
-// Bits of the nv A operand blocks that follow block tb in the ring of kABlocks.
-template <int kBlocks>
-__device__ __forceinline__ uint32_t block_mask(uint32_t tb, int nv)
-{
-    const uint32_t m = ((1u << nv) - 1u) << tb;
-    return (m | (m >> kBlocks)) & ((1u << kBlocks) - 1u);
-}
+static_assert((kABlocks & (kABlocks - 1)) == 0, "block and phase of a k-tile come from its sequence number by mask and shift");
 // A work item is a run of k-tiles of one 128-row block (and one activation tile column): a whole split-K
 // range, or, with the balanced schedule, a piece of one.
 __device__ __forceinline__ int ld_acquire_gpu(const int* p)
@@ -606,7 +598,6 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
 {
     // this width's k-tiles per stage and A operand blocks (they hide the file-scope defaults of the same names)
     constexpr int kKT = stage_kt(NPAD);
-    constexpr int kABlocks = a_blocks(NPAD);
     static_assert(kDecodeGroups >= kKT, "a stage must not give a group two k-tiles");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled activation tiles
@@ -635,7 +626,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
     // tiny N every instruction is pure latency, so the four k-steps of a k-tile go to different
     // accumulators (summed in the epilogue).
     constexpr int kNAcc = NPAD <= 16 ? 4 : NPAD <= 64 ? 2 : 1;
-    constexpr int kAccBufs = NPAD <= 32 || NPAD == 128 ? 2 : 1;
+    constexpr int kAccBufs = NPAD <= 128 ? 2 : 1;
     constexpr uint32_t kAccCols = kAccBufs * kNAcc * NPAD;
     constexpr uint32_t kACols = kABlocks * 32;
     static_assert(kAccCols + kACols <= 512, "TMEM budget");
@@ -921,7 +912,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
             // the decode groups that the block may be rewritten; the last one of a stage also arrives on
             // the stage's empty barrier, for the producers.
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            uint32_t idx = 0, slot = 0, sround = 0, tb = 0, ph = 0;  // tb: block of the stage's first k-tile
+            uint32_t idx = 0, slot = 0, sround = 0, tseq = 0;  // tseq: sequence number of the stage's first k-tile
             bool ok = true;
             Walk wk;
             wk.template init<kBalanced>(p);
@@ -942,9 +933,9 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                     const uint32_t sbase = stage0 + slot * stage_bytes;
                     ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_b + 8 * slot, sround & 1u, abort_flag));  // activation tiles
                     for (int sub = 0; sub < nv && ok; ++sub) {
-                        const uint32_t blk = (tb + (uint32_t)sub) % kABlocks;
+                        const uint32_t t = tseq + (uint32_t)sub, blk = t % kABlocks;
                         PROF_T(0);
-                        ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_aready + 8 * blk, (ph >> blk) & 1u, abort_flag));
+                        ok = __all_sync(0xffffffffu, mbar_wait_patient(bar_aready + 8 * blk, (t / kABlocks) & 1u, abort_flag));
                         if (!ok) break;
                         PROF_T(1);
                         tc_fence_after();
@@ -964,8 +955,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                         if (pacc[6] == 0 && lane == 0) { PROF_EV(5); pacc[6] = 1; }
 #endif
                     }
-                    ph ^= block_mask<kABlocks>(tb, nv);
-                    tb = (tb + (uint32_t)nv) % kABlocks;
+                    tseq += (uint32_t)nv;
                     if (++slot == (uint32_t)S) {
                         slot = 0;
                         ++sround;
@@ -1305,7 +1295,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
         const uint32_t rsel4 = 0x4440u | (uint32_t)(r_in_tile & 3);
         const uint32_t lutlane = smem_u32(smem + 1024 + kTileTabBytes * 4 * kDecodeGroups) + 8 * (uint32_t)(lane & 15);
 
-        uint32_t slot = 0, round = 0, rot = 0, tb = 0, ph = 0, used = 0;
+        uint32_t slot = 0, round = 0, rot = 0, tseq = 0;  // tseq: sequence number of the stage's first k-tile
         bool ok = true;
         Walk wk;
         wk.template init<kBalanced>(p);
@@ -1372,9 +1362,10 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
 #pragma unroll
                     for (int j = 0; j < kUnit; ++j) {
                         if (j >= nk || !ok) continue;
-                        const uint32_t blk = (tb + (uint32_t)(sub0 + j)) % kABlocks;
-                        // the MMAs of the block's previous k-tile
-                        if ((used >> blk) & 1u) ok = mbar_wait(bar_afree + 8 * blk, ((ph >> blk) & 1u) ^ 1u, abort_flag);
+                        const uint32_t t = tseq + (uint32_t)(sub0 + j), blk = t % kABlocks;
+                        // the MMAs of the block's previous k-tile (a barrier nobody has arrived on yet passes a wait
+                        // for the phase before its first, so the block's first use needs no special case)
+                        ok = mbar_wait(bar_afree + 8 * blk, ((t / kABlocks) & 1u) ^ 1u, abort_flag);
                         ok = __all_sync(0xffffffffu, ok);
                         if (!ok) continue;
                         tc_fence_after();
@@ -1407,10 +1398,7 @@ spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtenso
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
-                const uint32_t mask = block_mask<kABlocks>(tb, nv);
-                used |= mask;
-                ph ^= mask;
-                tb = (tb + (uint32_t)nv) % kABlocks;
+                tseq += (uint32_t)nv;
                 if (++slot == (uint32_t)S) {
                     slot = 0;
                     ++round;
