@@ -138,7 +138,8 @@ int spb_spmspm_bitmap_v3(void* stream, const uint16_t* Compressed_A, const int* 
  * call on a device raises the kernels' shared-memory limit (cudaFuncSetAttribute),
  * which spb_init also does.
  * N may be any positive value (the reference accepts only 8,16,32,64 and
- * multiples of 128; csrc/SpMM_API.cuh:60-96).  Returns a cudaError_t value;
+ * multiples of 128; csrc/SpMM_API.cuh:60-96): activation tiles of 16, 32, 64, 128 or 256
+ * columns, wider N is cut into tiles of 256 columns.  Returns a cudaError_t value;
  * invalid shapes give cudaErrorInvalidValue and launch nothing.
  */
 int spb_spmm_bitmap_v3(void* stream, const uint16_t* A, const uint16_t* Compressed_A, const int* TileOffsets,
@@ -172,11 +173,12 @@ int spb_spmm_bitmap_v3_noalloc(void* stream, const uint16_t* Compressed_A, const
 
 /*
  * One-time preparation of (current device, stream), no counterpart in the reference: raises the kernels'
- * shared-memory limit and creates the library-owned scratch (about 14 MB of partial sums and arrival counters)
- * that the balanced work schedule and the fused all-gather use on that stream.  Allocates device memory and
+ * shared-memory limit and creates the library-owned scratch (39 MB of fp32 partial sums and 4 MB of arrival
+ * counters) that the balanced work schedule, the split-K reduction fused into the SpMM kernel and the fused
+ * all-gather / all-reduce use on that stream.  Allocates device memory and
  * synchronises the device, so call it once per stream at start-up, outside stream capture (up to 8 streams per
- * device).  Without it every SpMM entry point still works, under the static schedule, and still allocates
- * nothing; spb_spmm_bitmap_v3_allgather needs it.
+ * device).  Without it every SpMM entry point still works, under the static schedule with a separate reduction
+ * launch, and still allocates nothing; spb_spmm_bitmap_v3_allgather and spb_spmm_bitmap_v3_allreduce need it.
  */
 int spb_init(void* stream);
 
@@ -217,7 +219,7 @@ unsigned long long spb_launch_count(void);
  *   SPB_SCHEDULE_STATIC: one work item per 128-row block and split-K range, no scratch.
  *   SPB_SCHEDULE_BALANCED: the k-tiles of all ranges are laid end to end and every SM takes an equal
  *     share; a range that is cut between SMs is summed in fp32 through scratch memory the library owns
- *     (about 14 MB per stream, created by spb_init), and rounded to fp16 once, where the reference
+ *     (39 MB per stream, created by spb_init), and rounded to fp16 once, where the reference
  *     rounds it.  The scratch belongs to the stream: a graph captured on a stream must not run at the
  *     same time as other calls made on that stream.  Calls on a stream spb_init was not called for, and
  *     spb_spmm_bitmap_v3_noalloc, use the static schedule.
