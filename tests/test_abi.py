@@ -135,3 +135,13 @@ def test_spmm_entry_points_reject_bad_arguments_without_launching(lib_built):
     assert lib.spb_linear_allreduce_finish(None, ok, ok, ok, 1, 128, 16, ok + 2, None, 0) == INVALID
     assert lib.spb_linear_allreduce_finish(None, ok, ok, ok, 1, 128, 16, None, None, 3) == INVALID
     assert lib.spb_linear_allreduce_finish(None, ok, ok, None, 1, 128, 16, None, None, 0) == INVALID
+
+
+def test_launch_counter_is_callable_without_a_gpu(lib_built):
+    from spmspm_b200 import _lib
+    lib = _lib.load()
+    n = lib.spb_launch_count()
+    assert isinstance(n, int) and n >= 0
+    # rejected calls launch nothing
+    assert lib.spb_spmm_bitmap_v3(None, None, None, None, None, None, None, None, None, 128, 16, 128, None, 1) != 0
+    assert lib.spb_launch_count() == n
