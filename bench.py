@@ -230,6 +230,9 @@ def main():
     ap.add_argument("--schedule", default="auto", choices=["auto", "static", "balanced"],
                     help="work schedule of the SpMM kernel (spb_set_schedule); auto lets the library choose per call")
     ap.add_argument("--no-extras", action="store_true", help="skip comparators, CPU baseline and encoder timing")
+    ap.add_argument("--spmspm", action="store_true",
+                    help="with --case on one GPU: the activations are pruned (50 %%) and passed bitmap-compressed in the "
+                         "second-operand layout (spb_spmspm_bitmap_v3, the fork's 19-argument form); N a multiple of 64")
     args = ap.parse_args()
     global SHAPES, NS, SPARSITY, WORKLOAD
     WORKLOAD = args.workload
@@ -307,6 +310,15 @@ def main():
     mat_sets = [mats] + [[clone(W) for W in mats] for _ in range(copies - 1)]
     rotating = copies * weight_bytes > 2 * l2_bytes
     acts = {(i, N): gen_act(N, K, i, dev) for i, (M, K) in enumerate(SHAPES) for N in NS}
+    acts_c = None
+    if args.spmspm:
+        if world > 1 or not args.case or any(N % 64 for N in NS):
+            print("[bench] --spmspm needs --case on one GPU with N a multiple of 64", file=sys.stderr)
+            sys.exit(2)
+        g = torch.Generator(device=dev).manual_seed(SEED + 77)
+        for k in acts:   # prune the activations (seeded Bernoulli, 50 %) and encode them in the second-operand layout
+            acts[k] = acts[k] * (torch.rand(acts[k].shape, device=dev, generator=g) >= 0.5)
+        acts_c = {k: sp.to_device(sp.init_sparse_matrix_a_bitmap_v6_b(v.cpu().numpy()), dev) for k, v in acts.items()}
     splits = {(i, N): forced_split or sp.suggest_split_k(mats[i].M, N, mats[i].K)
               for i in range(len(SHAPES)) for N in NS}
     outs = {(i, N): torch.empty((N, mats[i].M), dtype=torch.float16, device=dev) for (i, N) in acts}
@@ -340,6 +352,9 @@ def main():
     def step_local(c=0):
         for k in order:
             i, N = k
+            if acts_c is not None:
+                sp.spmspm(mat_sets[c][i], acts_c[k], split_k=splits[k], out=outs[k], workspace=ws)
+                continue
             sp.spmm(mat_sets[c][i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
             if world > 1:
                 dist.all_gather_into_tensor(gathered[k], outs[k])
@@ -539,6 +554,7 @@ def main():
                    "schedule": args.schedule,
                    "parallelism": f"tp{world}_m_split_allgather_{exchange}" if world > 1 else "single_gpu",
                    "l2": l2_note, "weight_copies": copies, "algorithmic_bytes_per_step": alg_bytes_step,
+                   "second_operand": "bitmap-compressed, 50 % pruned (spb_spmspm_bitmap_v3)" if acts_c is not None else "dense",
                    "launches_per_step": launches_per_step},
         "hbm_gbs": achieved * world if world > 1 else achieved,
         "e2e": {"value": flops_per_step() / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,

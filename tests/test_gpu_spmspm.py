@@ -63,6 +63,31 @@ def test_spmspm_has_the_bits_of_spmm_on_the_dense_operand(sp, M, K, N, sa, sb, s
     assert sp.device_status() == 0
 
 
+def test_spmspm_inside_a_cuda_graph(sp):
+    """The expansion buffer comes from the stream's memory pool, so the call can be captured and replayed."""
+    M, K, N = 512, 1024, 128
+    A = make_sparse(M, K, 0.6, seed=21)
+    B = make_sparse(N, K, 0.5, seed=22)
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    Bc = sp.to_device(sp.init_sparse_matrix_a_bitmap_v6_b(B))
+    want = sp.spmm(W, torch.from_numpy(B).cuda(), split_k=1)
+    out = torch.zeros((N, M), dtype=torch.float16, device="cuda")
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        sp.spmspm(W, Bc, split_k=1, out=out)
+        st.synchronize()
+        out.zero_()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            sp.spmspm(W, Bc, split_k=1, out=out)
+    for _ in range(3):
+        out.zero_()
+        gr.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), want.cpu().numpy().view(np.uint16))
+    assert sp.device_status() == 0
+
+
 def test_spmspm_rejects_bad_shapes_and_reports_corrupt_offsets(sp):
     A = make_sparse(256, 512, 0.6, 5)
     W = sp.encode_device(torch.from_numpy(A).cuda())
