@@ -521,6 +521,8 @@ def main():
         if not torch.allclose(got, want, atol=1e-2 * float(want.abs().max())):
             print("[bench] host-buffer pipeline result differs from the resident result", file=sys.stderr)
             sys.exit(1)
+        for hb in batches:
+            hb.close()
         e2e_how = ("HostBatch: packed copy in, graph of the step's SpMMs, packed copy out, double-buffered; wall clock "
                    "over the steps, host waits for every step's results")
     else:

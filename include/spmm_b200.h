@@ -176,11 +176,19 @@ int spb_spmm_bitmap_v3_noalloc(void* stream, const uint16_t* Compressed_A, const
  * shared-memory limit and creates the library-owned scratch (39 MB of fp32 partial sums and 4 MB of arrival
  * counters) that the balanced work schedule, the split-K reduction fused into the SpMM kernel and the fused
  * all-gather / all-reduce use on that stream.  Allocates device memory and
- * synchronises the device, so call it once per stream at start-up, outside stream capture (up to 8 streams per
- * device).  Without it every SpMM entry point still works, under the static schedule with a separate reduction
+ * synchronises the device, so call it once per stream at start-up, outside stream capture (up to 16 streams per
+ * device at a time, see spb_release).  Without it every SpMM entry point still works, under the static schedule with a separate reduction
  * launch, and still allocates nothing; spb_spmm_bitmap_v3_allgather and spb_spmm_bitmap_v3_allreduce need it.
  */
 int spb_init(void* stream);
+
+/*
+ * Gives back what spb_init created for (current device, stream): waits for the stream's work, then frees the scratch.
+ * For hosts that create and destroy streams over their lifetime (a device serves up to 16 initialised streams at a
+ * time; spb_init fails with cudaErrorMemoryAllocation beyond that, and SpMM calls on a stream without scratch use the
+ * static schedule).  Not during stream capture.  Returns 0 also when the stream had no scratch.
+ */
+int spb_release(void* stream);
 
 /*
  * Launch overlap of consecutive SpMM calls on one stream (no counterpart in the reference).  The SpMM kernel is

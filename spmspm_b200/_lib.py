@@ -42,6 +42,7 @@ SIGNATURES = {
     "spb_suggest_split_k": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "spb_set_schedule": (ctypes.c_int, [ctypes.c_int]),
     "spb_init": (ctypes.c_int, [_vp]),
+    "spb_release": (ctypes.c_int, [_vp]),
     "spb_set_weight_prefetch": (ctypes.c_int, [ctypes.c_int]),
     "spb_spmm_bitmap_v3_allgather": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_int, ctypes.c_int,
                                                     ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _vp, ctypes.c_int]),

@@ -291,12 +291,29 @@ def init(stream=None):
         _initialised.add(key)
 
 
+def release(stream=None):
+    """spb_release: give back the scratch `init` created for the current device and `stream` (waits for the stream)."""
+    s = stream if stream is not None else torch.cuda.current_stream()
+    _check(_lib.load().spb_release(ctypes.c_void_p(s.cuda_stream)), "spb_release")
+    _initialised.discard((torch.cuda.current_device(), s.cuda_stream))
+    _no_scratch.discard((torch.cuda.current_device(), s.cuda_stream))
+
+
+_no_scratch = set()
+
+
 def _init_if_possible(stream):
     """The Python wrappers prepare a stream the first time they see it, unless it is being captured (the C entry
-    points never do: they fall back to the static schedule on a stream spb_init was not called for)."""
+    points never do: they fall back to the static schedule on a stream spb_init was not called for).  When the
+    device's scratch sets are all taken the stream simply stays without one: the calls then run the static schedule."""
     s = stream if stream is not None else torch.cuda.current_stream()
-    if (torch.cuda.current_device(), s.cuda_stream) not in _initialised and not torch.cuda.is_current_stream_capturing():
+    key = (torch.cuda.current_device(), s.cuda_stream)
+    if key in _initialised or key in _no_scratch or torch.cuda.is_current_stream_capturing():
+        return
+    try:
         init(s)
+    except SpmmError:
+        _no_scratch.add(key)
 
 
 def suggest_split_k(M, N, K):

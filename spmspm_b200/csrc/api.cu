@@ -498,6 +498,8 @@ unsigned long long spb_launch_count(void) { return spb::g_launches.load(); }
 
 int spb_init(void* stream) { return (int)spb::init_stream((cudaStream_t)stream); }
 
+int spb_release(void* stream) { return (int)spb::release_stream((cudaStream_t)stream); }
+
 int spb_set_weight_prefetch(int on) { return spb::set_weight_prefetch(on); }
 
 int spb_set_schedule(int mode)

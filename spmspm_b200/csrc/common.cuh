@@ -79,6 +79,7 @@ cudaError_t wait_flags_launch(cudaStream_t s, uint32_t* flags, int n, int* statu
 cudaError_t exchange_counter(cudaStream_t s, int** out);  // a zeroed int of the stream's scratch, for CTA counting
 cudaError_t spmm_launch(cudaStream_t s, const SpmmArgs& a);
 cudaError_t init_stream(cudaStream_t s);  // scratch of the balanced schedule / fused exchange for this stream
+cudaError_t release_stream(cudaStream_t s);  // gives that scratch back (synchronises the stream)
 int suggest_split_k(int M, int N, int K);
 // Work schedule of the SpMM kernel: 1 = static (one work item per split-K range, no scratch), 2 = balanced
 // (equal k-tile shares per SM, fp32 exchange through library-owned scratch) whenever possible, 0 = whichever

@@ -1484,7 +1484,7 @@ DeviceInfo device_info()
 // entry points themselves never allocate or synchronise (the reference's entry point is asynchronous and
 // allocation-free, reference csrc/SpMM_API.cuh:47-110); on a stream that was never initialised they use
 // the static schedule, which needs no scratch.
-constexpr int kScratchSets = 8;
+constexpr int kScratchSets = 16;
 constexpr int kCounterCap = 1 << 20;
 struct ScratchSet {
     float* partials = nullptr;
@@ -1811,6 +1811,30 @@ cudaError_t init_stream(cudaStream_t s)
     if (!scratch_for(s, dev, di.sms, true)) {
         set_error("spb_init: no scratch set left (%d streams per device) or out of device memory", kScratchSets);
         return cudaErrorMemoryAllocation;
+    }
+    return cudaSuccess;
+}
+
+// Gives back the scratch spb_init created for (current device, stream), after the stream's work has completed.
+cudaError_t release_stream(cudaStream_t s)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (stream_is_capturing(s)) {
+        set_error("spb_release: the stream is being captured");
+        return cudaErrorStreamCaptureUnsupported;
+    }
+    e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    for (int i = 0; i < kScratchSets; ++i) {
+        ScratchSet& set = g_scratch[dev][i];
+        if (!set.taken || set.stream != s) continue;
+        cudaFree(set.partials);
+        cudaFree(set.counters);
+        set = ScratchSet();
     }
     return cudaSuccess;
 }

@@ -97,5 +97,12 @@ class HostBatch:
             if busy:
                 stream.wait_event(self.ev_out[s])
 
+    def close(self):
+        """Wait for everything submitted and give the compute stream's scratch back to the library."""
+        for s in range(len(self._busy)):
+            self.wait(s)
+        with torch.cuda.device(self.device):
+            api.release(self.s_run)
+
     def bytes_per_batch(self):
         return 2 * self.h_in[0].numel(), 2 * self.h_out[0].numel()

@@ -33,6 +33,7 @@ def test_host_batch_matches_resident_spmm(lib_built):
                 assert np.array_equal(out.numpy().view(np.uint16), want.cpu().numpy().view(np.uint16))
                 ref = oracle.gemm_f32(A, B)
                 assert float(np.abs(out.numpy().astype(np.float32) - ref).max()) <= 1e-2 * float(np.abs(ref).max())
+    hb.close()
     h2d, d2h = hb.bytes_per_batch()
     assert h2d == 2 * sum(N * K for (M, K, N) in shapes) and d2h == 2 * sum(N * M for (M, K, N) in shapes)
     assert sp.device_status() == 0

@@ -3,6 +3,8 @@
 Tolerance (fp16 output, fp32 accumulation): max |c - ref| <= 1e-2 * max|ref| and element-wise
 |c - ref| <= 1e-2 * |ref| + 1e-2 * rms(ref), ref = fp32 host GEMM.
 """
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -297,4 +299,49 @@ def test_entry_point_allocates_nothing_until_spb_init(sp):
         _assert_close(out.cpu().numpy(), ref)
     finally:
         sp.set_schedule(sp.SCHEDULE_AUTO)
+    assert sp.device_status() == 0
+
+
+def test_more_streams_than_scratch_sets_and_release(sp):
+    """A process that keeps creating streams: once the device's scratch sets are taken, calls on further streams run
+    the static schedule (no error, same tolerance); spb_release gives a set back."""
+    from spmspm_b200 import _lib
+    A = make_sparse(512, 1024, 0.6, seed=301)
+    B = torch.from_numpy(make_dense(16, 1024, seed=302)).cuda()
+    W = sp.encode_device(torch.from_numpy(A).cuda())
+    ref = oracle.gemm_f32(A, B.cpu().numpy())
+    scale = float(np.abs(ref).max())
+    streams = [torch.cuda.Stream(priority=p) for p in (0, -1) for _ in range(20)]   # torch hands out pooled streams
+    seen = set()
+    for st in streams:
+        with torch.cuda.stream(st):
+            got = sp.spmm(W, B, split_k=2)
+        st.synchronize()
+        seen.add(st.cuda_stream)
+        assert float(np.abs(got.cpu().numpy().astype(np.float32) - ref).max()) <= 1e-2 * scale
+    lib = _lib.load()
+    for st in streams:                                       # give back whatever these streams took
+        sp.release(st)
+    sp.release(torch.cuda.current_stream())                  # at least one set is free now
+    try:
+        cudart = ctypes.CDLL("libcudart.so.12")
+    except OSError:
+        cudart = ctypes.CDLL("libcudart.so")
+    extra, refused = [], None
+    for _ in range(40):                                      # raw streams until spb_init refuses
+        h = ctypes.c_void_p()
+        assert cudart.cudaStreamCreate(ctypes.byref(h)) == 0
+        if lib.spb_init(h) != 0:
+            refused = h
+            break
+        extra.append(h)
+    assert refused is not None and len(extra) >= 1 and b"no scratch set left" in lib.spb_last_error()
+    assert lib.spb_release(extra[0]) == 0
+    assert lib.spb_init(refused) == 0                        # the freed set goes to the stream that was refused
+    for h in extra + [refused]:
+        assert lib.spb_release(h) == 0
+        assert cudart.cudaStreamDestroy(h) == 0
+    got = sp.spmm(W, B, split_k=2)                           # the default stream gets a set again on its next call
+    torch.cuda.synchronize()
+    assert float(np.abs(got.cpu().numpy().astype(np.float32) - ref).max()) <= 1e-2 * scale
     assert sp.device_status() == 0
