@@ -579,7 +579,7 @@ def main():
     if exchange_probe:
         line["exchange_probe_ms_per_step"] = exchange_probe
     if world == 1 and not args.no_extras:
-        line["comparators"] = {"cublas_dense_fp16": cublas_dense(dev, acts, order, args)}
+        line["comparators"] = {"cublas_dense_fp16": cublas_dense(dev, acts, order, args, ours=outs)}
         rs = ref_style(dev, sp, mats, acts, order, args)
         if rs is not None:
             line["comparators"]["reference_style_mma_sync"] = rs
@@ -669,9 +669,11 @@ def graph_time(fn, args):
     return e0.elapsed_time(e1) / args.steps
 
 
-def cublas_dense(dev, acts, order, args):
+def cublas_dense(dev, acts, order, args, ours=None):
     """Dense fp16 GEMM (cuBLAS through torch.mm, fp32 accumulate) on the un-compressed pruned weights, same shapes,
-    same rotation over the matrices; the comparator the reference's drivers use (csrc/spmm_test.cu:101-102)."""
+    same rotation over the matrices; the comparator the reference's drivers use (csrc/spmm_test.cu:101-102).  With
+    `ours` (this library's outputs of the same SpMMs) also the figure those drivers print: TotalError, the sum over
+    all outputs of |cuBLAS - other| (csrc/spmm_test_utils.h:110-115), here summed over the SpMMs of the step."""
     dense = [gen_weight(M, K, i, dev) for i, (M, K) in enumerate(SHAPES)]
     outs = {k: torch.empty((k[1], SHAPES[k[0]][0]), dtype=torch.float16, device=dev) for k in order}
 
@@ -681,8 +683,16 @@ def cublas_dense(dev, acts, order, args):
 
     ms = graph_time(step, args)
     dense_bytes = sum(2 * SHAPES[i][0] * SHAPES[i][1] for (i, N) in order)
-    return {"value": flops_per_step() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
-            "dense_weight_gbs": dense_bytes / (ms * 1e-3) / 1e9}
+    res = {"value": flops_per_step() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+           "dense_weight_gbs": dense_bytes / (ms * 1e-3) / 1e9}
+    if ours is not None:
+        step()
+        torch.cuda.synchronize()
+        total = sum(float((outs[k].float() - ours[k].float()).abs().sum()) for k in order)
+        count = sum(outs[k].numel() for k in order)
+        res["total_error_vs_this_library"] = total
+        res["mean_abs_error_vs_this_library"] = total / count
+    return res
 
 
 def ref_style(dev, sp, mats, acts, order, args):
