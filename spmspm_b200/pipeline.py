@@ -38,7 +38,8 @@ class HostBatch:
         self._busy = [False] * sets
         self.graphs = []
         with torch.cuda.device(self.device):
-            api.init(self.s_run)
+            with torch.cuda.stream(self.s_run):
+                api._init_if_possible(self.s_run)   # without a free scratch set the batch runs the static schedule
             for s in range(sets):
                 with torch.cuda.stream(self.s_run):
                     self._enqueue(s)                      # warm-up outside capture
