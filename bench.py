@@ -465,70 +465,78 @@ def main():
 
     # ---- end to end through the C ABI with host buffers: activations in, outputs back, every SpMM
     h_acts = {k: v.cpu().pin_memory() for k, v in acts.items()}
-    h_outs = {k: torch.empty((k[1], SHAPES[k[0]][0]), dtype=torch.float16).pin_memory() for k in acts}
-    d_full = {k: torch.empty((k[1], SHAPES[k[0]][0]), dtype=torch.float16, device=dev) for k in acts}
+    # The package's host-buffer front end (spmspm_b200.pipeline.HostBatch): per step one packed copy of the step's
+    # activations from pinned host memory, the step's SpMMs (several GPUs: row shards + exchange, every rank ends up
+    # with all rows), one packed copy of the results back to pinned host memory; two staging sets, so the copies of one
+    # step overlap the SpMMs of the next.  Every step's inputs are written into the pinned buffer and every step's
+    # results are waited for on the host.
+    from spmspm_b200.pipeline import HostBatch
+    streams = tuple(torch.cuda.Stream(dev) for _ in range(3))
+    full_cols = [SHAPES[i][0] for (i, N) in order]
+    e2e_copies = copies if world == 1 else 1     # several GPUs: one weight copy (buffers of the exchange per staging set)
+    bodies = [None] * e2e_copies
+    if world > 1:
+        e2e_peer = None
+        if exchange == "peer":
+            # buffers of their own per staging set: a set is resubmitted only after every rank has been seen to finish
+            # the set between, whose SpMMs run after this rank's copies out of the first
+            e2e_peer = [{k: spd.PeerGather(k[1], SHAPES[k[0]][0], dev, slots=1) for k in order} for _ in range(2)]
+        e2e_gathered = {k: torch.empty((world, k[1], mats[k[0]].M), dtype=torch.float16, device=dev) for k in order}
+
+        def body(s, ins, outs_v):
+            if e2e_peer is not None:
+                for k, x in zip(order, ins):
+                    e2e_peer[s][k].spmm(mat_sets[0][k[0]], x, row_lo[k[0]], split_k=splits[k], workspace=ws)
+                for k, y in zip(order, outs_v):
+                    y.copy_(e2e_peer[s][k].wait())
+            else:
+                for k, x, y in zip(order, ins, outs_v):
+                    sp.spmm(mat_sets[0][k[0]], x, split_k=splits[k], out=outs[k], workspace=ws)
+                    dist.all_gather_into_tensor(e2e_gathered[k], outs[k])
+                    y.copy_(e2e_gathered[k].permute(1, 0, 2).reshape(k[1], -1))
+        bodies = [body]
+    batches = [HostBatch([(mat_sets[c][i], N) for (i, N) in order], dev, split_k=[splits[k] for k in order],
+                         streams=streams, body=bodies[c], out_cols=full_cols, ready=sync_all if world > 1 else None)
+               for c in range(e2e_copies)]
+    for hb in batches:
+        for s_ in range(2):
+            for view, k in zip(hb.inputs(s_), order):
+                view.copy_(h_acts[k])
+    state = {"prev": None}
 
     def e2e_step(it):
-        c = it % copies
-        for k in order:
-            i, N = k
-            acts[k].copy_(h_acts[k], non_blocking=True)
-            sp.spmm(mat_sets[c][i], acts[k], split_k=splits[k], out=outs[k], workspace=ws)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[k], outs[k])
-                d_full[k].copy_(gathered[k].permute(1, 0, 2).reshape(N, -1))
-                h_outs[k].copy_(d_full[k], non_blocking=True)
-            else:
-                h_outs[k].copy_(outs[k], non_blocking=True)
+        hb, s_ = batches[it % e2e_copies], (it // e2e_copies) % 2
+        hb.submit(s_)
+        if state["prev"] is not None:
+            state["prev"][0].wait(state["prev"][1])      # the host reads the previous step's results
+        state["prev"] = (hb, s_)
+
+    def e2e_timed(steps):
+        sync_all()
+        t0 = time.perf_counter()
+        for i_ in range(steps):
+            e2e_step(i_)
+        state["prev"][0].wait(state["prev"][1])
         torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
-    e2e_how = "per SpMM: copy in, spmm, gather, copy out, on one stream"
-    if world == 1:
-        # One GPU: the package's host-buffer front end (spmspm_b200.pipeline.HostBatch): per step one packed copy of
-        # the step's activations from pinned host memory, the step's SpMMs, one packed copy of the results back to
-        # pinned host memory; two staging sets, so the copies of one step overlap the SpMMs of the next.  Every
-        # step's inputs are written into the pinned buffer and every step's results are waited for on the host.
-        from spmspm_b200.pipeline import HostBatch
-        streams = tuple(torch.cuda.Stream(dev) for _ in range(3))
-        batches = [HostBatch([(mat_sets[c][i], N) for (i, N) in order], dev, split_k=[splits[k] for k in order],
-                             streams=streams) for c in range(copies)]
-        for hb in batches:
-            for s in range(2):
-                for view, k in zip(hb.inputs(s), order):
-                    view.copy_(h_acts[k])
-        state = {"prev": None}
-
-        def e2e_step(it):
-            hb, s = batches[it % copies], (it // copies) % 2
-            hb.submit(s)
-            if state["prev"] is not None:
-                state["prev"][0].wait(state["prev"][1])      # the host reads the previous step's results
-            state["prev"] = (hb, s)
-
-        def e2e_timed(steps):
-            sync_all()
-            t0 = time.perf_counter()
-            for i in range(steps):
-                e2e_step(i)
-            state["prev"][0].wait(state["prev"][1])
-            torch.cuda.synchronize()
-            return (time.perf_counter() - t0) * 1e3
-
-        e2e_timed(3)
-        e2e_ms = e2e_timed(args.steps) / args.steps
-        got = batches[0].outputs(0)[0].float()
-        want = outs[order[0]].float().cpu()
-        if not torch.allclose(got, want, atol=1e-2 * float(want.abs().max())):
-            print("[bench] host-buffer pipeline result differs from the resident result", file=sys.stderr)
-            sys.exit(1)
-        for hb in batches:
-            hb.close()
-        e2e_how = ("HostBatch: packed copy in, graph of the step's SpMMs, packed copy out, double-buffered; wall clock "
-                   "over the steps, host waits for every step's results")
-    else:
-        for it in range(3):
-            e2e_step(it)
-        e2e_ms = timed(e2e_step, args.steps) / args.steps
+    e2e_timed(3)
+    e2e_ms = e2e_timed(args.steps) / args.steps
+    got = batches[0].outputs(0)[0].float()
+    want = full_output(order[0]).float().cpu()
+    if not torch.allclose(got, want, atol=1e-2 * float(want.abs().max())):
+        print("[bench] host-buffer pipeline result differs from the resident result", file=sys.stderr)
+        sys.exit(1)
+    for hb in batches:
+        hb.close()
+    e2e_how = ("HostBatch: packed copy in, graph of the step's SpMMs" + (" and their exchange" if world > 1 else "") +
+               ", packed copy out, double-buffered; wall clock over the steps (max over ranks), host waits for every "
+               "step's results")
     h2d = sum(N * SHAPES[i][1] * 2 for (i, N) in order)
     d2h = sum(N * SHAPES[i][0] * 2 for (i, N) in order)
 

@@ -15,16 +15,23 @@ from . import api
 
 
 class HostBatch:
-    def __init__(self, items, device, split_k=None, sets=2, streams=None):
+    def __init__(self, items, device, split_k=None, sets=2, streams=None, body=None, out_cols=None, ready=None):
         """items: list of (BitmapMatrix W, N); split_k: optional list of Split_K values (default: the library's);
         streams: (copy-in, compute, copy-out) streams to share with other batches (default: three new ones; every
-        compute stream takes one of the library's per-stream scratch sets)."""
+        compute stream takes one of the library's per-stream scratch sets).
+        body(s, ins, outs): replaces the plain loop of SpMMs for staging set s (ins / outs: the device views of the
+        packed buffers), e.g. SpMMs of row shards followed by an exchange between GPUs; it is captured into the set's
+        graph.  out_cols: result columns per item when they differ from W.M (gathered rows of a sharded weight).
+        ready(): called after the buffers exist and before each set's first (uncaptured) run, e.g. a barrier between
+        the processes of a body that exchanges data, whose device-side waits are bounded."""
         self.device = torch.device(device)
         self.items = list(items)
         self.split_k = [sk if sk else api.suggest_split_k(W.M, N, W.K)
                         for (W, N), sk in zip(self.items, split_k or [None] * len(self.items))]
         n_in = sum(N * W.K for W, N in self.items)
-        n_out = sum(N * W.M for W, N in self.items)
+        self.out_cols = list(out_cols) if out_cols is not None else [W.M for W, N in self.items]
+        self.body = body
+        n_out = sum(N * m for (W, N), m in zip(self.items, self.out_cols))
         ws_elems = max([sk * N * W.M for (W, N), sk in zip(self.items, self.split_k) if sk > 1] or [8])
         self.h_in = [torch.empty(n_in, dtype=torch.float16).pin_memory() for _ in range(sets)]
         self.h_out = [torch.empty(n_out, dtype=torch.float16).pin_memory() for _ in range(sets)]
@@ -41,6 +48,8 @@ class HostBatch:
             with torch.cuda.stream(self.s_run):
                 api._init_if_possible(self.s_run)   # without a free scratch set the batch runs the static schedule
             for s in range(sets):
+                if ready is not None:
+                    ready()
                 with torch.cuda.stream(self.s_run):
                     self._enqueue(s)                      # warm-up outside capture
                 self.s_run.synchronize()
@@ -49,24 +58,26 @@ class HostBatch:
                     self._enqueue(s)
                 self.graphs.append(g)
 
-    def _views(self, flat, cols_of):
+    def _views(self, flat, cols):
         out, at = [], 0
-        for W, N in self.items:
-            n = N * cols_of(W)
-            out.append(flat[at:at + n].view(N, cols_of(W)))
-            at += n
+        for (W, N), c in zip(self.items, cols):
+            out.append(flat[at:at + N * c].view(N, c))
+            at += N * c
         return out
 
     def inputs(self, s):
         """Host views [N, K] of set s's packed activation buffer, one per item: the caller writes them."""
-        return self._views(self.h_in[s], lambda W: W.K)
+        return self._views(self.h_in[s], [W.K for W, N in self.items])
 
     def outputs(self, s):
         """Host views [N, M] of set s's packed result buffer, valid after wait(s)."""
-        return self._views(self.h_out[s], lambda W: W.M)
+        return self._views(self.h_out[s], self.out_cols)
 
     def _enqueue(self, s):
-        ins, outs = self._views(self.d_in[s], lambda W: W.K), self._views(self.d_out[s], lambda W: W.M)
+        ins, outs = self._views(self.d_in[s], [W.K for W, N in self.items]), self._views(self.d_out[s], self.out_cols)
+        if self.body is not None:
+            self.body(s, ins, outs)
+            return
         for (W, N), sk, x, y in zip(self.items, self.split_k, ins, outs):
             api.spmm(W, x, split_k=sk, out=y, workspace=self.ws)
 
