@@ -37,3 +37,34 @@ def test_host_batch_matches_resident_spmm(lib_built):
     h2d, d2h = hb.bytes_per_batch()
     assert h2d == 2 * sum(N * K for (M, K, N) in shapes) and d2h == 2 * sum(N * M for (M, K, N) in shapes)
     assert sp.device_status() == 0
+
+
+def test_host_batch_with_a_custom_body(lib_built):
+    """The batch's work can be any sequence enqueued on the compute stream (here: linear layers with bias and ReLU)."""
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import spmspm_b200 as sp
+    from spmspm_b200.pipeline import HostBatch
+    shapes = [(512, 1024, 16), (256, 1024, 16)]
+    As = [make_sparse(M, K, 0.6, seed=7 * M) for (M, K, N) in shapes]
+    Ws = [sp.encode_device(torch.from_numpy(A).cuda()) for A in As]
+    biases = [torch.randn(M, device="cuda").half() for (M, K, N) in shapes]
+    called = []
+
+    def body(s, ins, outs):
+        called.append(s)
+        for W, b, x, y in zip(Ws, biases, ins, outs):
+            sp.linear(W, x, bias=b, activation=sp.ACT_RELU, split_k=1, out=y)
+
+    hb = HostBatch([(W, N) for W, (M, K, N) in zip(Ws, shapes)], "cuda", body=body, ready=lambda: None)
+    assert sorted(set(called)) == [0, 1]
+    Bs = [make_dense(N, K, seed=50 + i) for i, (M, K, N) in enumerate(shapes)]
+    for view, B in zip(hb.inputs(1), Bs):
+        view.copy_(torch.from_numpy(B))
+    hb.submit(1)
+    hb.wait(1)
+    for out, W, b, B in zip(hb.outputs(1), Ws, biases, Bs):
+        want = torch.relu(sp.spmm(W, torch.from_numpy(B).cuda(), split_k=1) + b)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.numpy().view(np.uint16), want.cpu().numpy().view(np.uint16))
+    hb.close()
+    assert sp.device_status() == 0
