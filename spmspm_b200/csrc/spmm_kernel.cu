@@ -70,13 +70,15 @@ namespace {
 // them.)  Activation tiles wider than 64 columns leave room for two k-tiles per stage only (stage_kt).
 constexpr int kKT = 4;
 __host__ __device__ constexpr int stage_kt(int npad) { return npad > 64 ? 2 : 4; }
-#ifndef SPB_GROUPS
-#define SPB_GROUPS 4
-#endif
 // Decode groups.  The k-tiles of the CTA's whole sequence are dealt to the groups in turn (k-tile t goes to
-// group t % kDecodeGroups), so a stage gives a group at most one k-tile as long as there are at least kKT groups.
-constexpr int kDecodeGroups = SPB_GROUPS;
-static_assert(kDecodeGroups >= kKT && kDecodeGroups <= 6, "a stage must not give a group two k-tiles; 32 warps at most");
+// group t % groups), so a stage gives a group at most one k-tile as long as there are at least kKT groups.
+// Six groups at 64 registers per thread (nobody resizes) for activation tiles up to 64 columns, four at 96 registers
+// for the wide tiles (measured: six groups are 2-6 % faster up to 64 columns, 19 % slower at 128).
+#ifdef SPB_GROUPS
+__host__ __device__ constexpr int decode_groups(int) { return SPB_GROUPS; }
+#else
+__host__ __device__ constexpr int decode_groups(int npad) { return npad <= 64 ? 6 : 4; }
+#endif
 // A operand blocks in tensor memory (32 columns = one k-tile each), used in turn: k-tile t uses block t % kABlocks.
 // Eight blocks, two per decode group: a group can start its next k-tile while the tensor core still reads its last
 // one.  A power of two, so that block and barrier phase of the t-th k-tile of the CTA's sequence are t % 8 and
@@ -85,21 +87,15 @@ constexpr int kABlocks = 8;
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kDecodeWarp0 = 8;
-constexpr int kThreads = 32 * (kDecodeWarp0 + 4 * kDecodeGroups);
-// Registers per thread after the roles have resized.  A CTA owns the registers it was launched with,
-// kRegsLaunch per thread (65536 / kThreads rounded down to a multiple of 8, what ptxas reports for the
-// kernel), and a warp that grows can only take what other warps of the CTA have given back: if the sizes
-// below added up to more than the launch allocation, the last warps to grow would block for ever.
-constexpr int kRegsLaunch = 65536 / kThreads / 8 * 8;
-constexpr int kRegsControl = 40, kRegsEpilogue = 56;
-constexpr int kRegsDecode = kDecodeGroups == 4 ? 96 : kDecodeGroups == 5 ? 80 : 64;
-static_assert(kRegsControl % 8 == 0 && kRegsEpilogue % 8 == 0 && kRegsDecode % 8 == 0, "register counts come in eights");
-static_assert(128 * kRegsControl + 128 * kRegsEpilogue + 128 * kDecodeGroups * kRegsDecode <= kRegsLaunch * kThreads,
-              "register budget: the resized roles must fit into the CTA's launch allocation");
-static_assert(kRegsControl <= kRegsLaunch && kRegsEpilogue <= kRegsLaunch && kRegsDecode >= kRegsLaunch,
-              "roles that shrink must not exceed, roles that grow must not undercut the launch allocation");
+__host__ __device__ constexpr int threads_for(int npad) { return 32 * (kDecodeWarp0 + 4 * decode_groups(npad)); }
+// Registers per thread after the roles have resized.  A CTA owns the registers it was launched with
+// (65536 / threads rounded down to a multiple of 8 per thread, what ptxas reports for the kernel), and a warp
+// that grows can only take what other warps of the CTA have given back: if the sizes below added up to more
+// than the launch allocation, the last warps to grow would block for ever (checked at compile time in the kernel).
 // With six groups the launch allocation (64 registers) is what the decode loop needs: nobody resizes.
-constexpr bool kResize = kRegsDecode > kRegsLaunch;
+constexpr int kRegsControl = 40, kRegsEpilogue = 56;
+__host__ __device__ constexpr int regs_launch(int groups) { return 65536 / (32 * (kDecodeWarp0 + 4 * groups)) / 8 * 8; }
+__host__ __device__ constexpr int regs_decode(int groups) { return groups == 4 ? 96 : groups == 5 ? 80 : 64; }
 constexpr int kMaxPeers = 8;
 constexpr int kMaxStages = 24;
 // Shared-memory header: barriers and flags (1 KB), one tile table per decode warp, then the selector table.
@@ -110,8 +106,7 @@ constexpr int kMaxStages = 24;
 constexpr int kUnit = SPB_UNIT;
 constexpr int kTileTabBytes = 512 * kUnit;
 constexpr int kLutBytes = 256 * 16 * 8;
-constexpr int kHeaderBytes = 1024 + kTileTabBytes * 4 * kDecodeGroups + kLutBytes;
-static_assert(kHeaderBytes % 1024 == 0, "the stages behind the header must stay 1024-byte aligned");
+__host__ __device__ constexpr int header_bytes(int groups) { return 1024 + kTileTabBytes * 4 * groups + kLutBytes; }
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 
@@ -593,12 +588,23 @@ __device__ __forceinline__ void unit_expand(const UnitLoads& u, uint32_t* o)
 // slower on calls that never used it).  kBalanced: the work schedule (see Walk); the static variant carries
 // no code for the exchange of partial sums.
 template <int NPAD, bool kExchange, bool kBalanced>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_for(NPAD), 1)
 spmm_bitmap_tcgen05_kernel(const KernelParams p, const __grid_constant__ CUtensorMap tmap_b)
 {
     // this width's k-tiles per stage and A operand blocks (they hide the file-scope defaults of the same names)
     constexpr int kKT = stage_kt(NPAD);
-    static_assert(kDecodeGroups >= kKT, "a stage must not give a group two k-tiles");
+    constexpr int kDecodeGroups = decode_groups(NPAD);
+    constexpr int kThreads = threads_for(NPAD);
+    constexpr int kRegsLaunch = regs_launch(kDecodeGroups), kRegsDecode = regs_decode(kDecodeGroups);
+    constexpr bool kResize = kRegsDecode > kRegsLaunch;
+    constexpr int kHeaderBytes = header_bytes(kDecodeGroups);
+    static_assert(kDecodeGroups >= kKT && kDecodeGroups <= 6, "a stage must not give a group two k-tiles; 32 warps at most");
+    static_assert(kRegsControl % 8 == 0 && kRegsEpilogue % 8 == 0 && kRegsDecode % 8 == 0, "register counts come in eights");
+    static_assert(!kResize || 128 * kRegsControl + 128 * kRegsEpilogue + 128 * kDecodeGroups * kRegsDecode <= kRegsLaunch * kThreads,
+                  "register budget: the resized roles must fit into the CTA's launch allocation");
+    static_assert(!kResize || (kRegsControl <= kRegsLaunch && kRegsEpilogue <= kRegsLaunch && kRegsDecode >= kRegsLaunch),
+                  "roles that shrink must not exceed, roles that grow must not undercut the launch allocation");
+    static_assert(kHeaderBytes % 1024 == 0, "the stages behind the header must stay 1024-byte aligned");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled activation tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1745,7 +1751,7 @@ cudaError_t launch_t(cudaStream_t s, const SpmmArgs& a, const DeviceInfo& di, in
     // kernel; the kernel itself waits for that kernel before it touches global memory.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(threads_for(NPAD));
     cfg.dynamicSmemBytes = (size_t)dyn_smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
