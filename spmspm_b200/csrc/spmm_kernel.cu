@@ -6,22 +6,27 @@
 //   producer warps  three warps stream the compressed weight (packed values; bitmaps and median
 //                   offsets; activation tiles) of two vertically adjacent 64x64 global tiles with
 //                   1-D bulk copies and the activation tile with a 2-D TMA load into a ring of
-//                   shared-memory stages of four k-tiles each, completion on mbarriers;
-//   decode warps    (4 groups of 4 warps, one group per k-tile of a stage, one thread per weight
+//                   shared-memory stages of four k-tiles each (two for activation tiles of 128 and
+//                   256 columns), completion on mbarriers;
+//   decode warps    (6 groups of 4 warps for activation tiles up to 64 columns, 4 groups for the
+//                   wide tiles; the k-tiles are dealt to the groups in turn, one thread per weight
 //                   row) expand the bitmaps: per k-tile a warp first works out where the values of
 //                   its 32 tiles start (one tile per lane: population count of the bitmap, prefix
 //                   sum over the 16 tiles of a median tile by shuffles), then every thread, for
 //                   each of the 8 tiles its row crosses, finds its row's values with population
-//                   counts, expands them with byte permutes driven by two nibble tables and writes
+//                   counts, expands them with byte permutes driven by a selector table and writes
 //                   the dense 128 x 64 fp16 tile straight into tensor memory (tcgen05.st) as the
 //                   MMA's A operand.  Every k-tile's A operand block has its own ready/free
 //                   barriers, so a group only ever waits for the tensor core's work on its own
 //                   k-tiles;
-//   MMA warp        one thread issues tcgen05.mma (M=128, N=16..64, K=16, fp16 in,
+//   MMA warp        one thread issues tcgen05.mma (M=128, N=16..256, K=16, fp16 in,
 //                   fp32 accumulate in TMEM), A from TMEM, B from the swizzled smem tile;
 //   epilogue warps  read the accumulator (tcgen05.ld), round to fp16 and store C or the
 //                   split-K partial, column-major as the reference does
-//                   (reference csrc/SpMM_Kernel.cuh:192-198).
+//                   (reference csrc/SpMM_Kernel.cuh:192-198); under the static schedule the last
+//                   CTA of a row block also sums the split-K partials (the reference's
+//                   SplitK_Reduction, csrc/Reduction_Kernel.cuh:24-44); the exchange variants add
+//                   the element-wise tail of a linear layer and the stores to other GPUs' buffers.
 //
 // Work is scheduled in one of two ways (see Walk).  Static: a work item is (row block of 128 rows,
 // split-K range), the ranges cut exactly like the reference's (reference csrc/SpMM_Kernel.cuh:35-43),
